@@ -33,6 +33,27 @@ int  nt_model_finalize(nt_model_t m);
 void nt_model_free(nt_model_t m);
 int  nt_model_get_config(nt_model_t m, nt_model_config* out);
 
+/* Model folders (config.json + model.safetensors) of a registered layer-spec family; exact_f32: everything in true 32-bit. */
+nt_model_t nt_model_load_dir(const char* dir, int max_context, int exact_f32);
+/* The same family from a config.json TEXT and caller-owned device tensors: create_json -> set_tensor (checkpoint names; matrices
+ * F32 / F16 / BF16 row-major, gain vectors F32) -> finalize. */
+nt_model_t nt_model_create_json(const char* config_json, int max_context, int exact_f32);
+/* forward + the logits at the wanted places (ascending indices into the tokens) -> logits_host [n_want, vocab] */
+int  nt_model_forward_logits(nt_model_t m, const int* tokens_host, int seq_len, int start_pos, const int* want, int n_want, float* logits_host);
+/* Engine: load a GGUF file or a model folder; generate over token ids (returns the number generated, ids in out_ids[0..cap)) */
+int  nt_engine_load_path(void* engine, const char* path, int max_context, int exact_f32);
+int  nt_engine_generate_ids(void* engine, const int* prompt_ids, int n_prompt, int max_tokens, float temperature, int top_k, float top_p,
+                            float repeat_penalty, unsigned long long seed, int* out_ids, int cap);
+/* Kernels of the layer-spec mechanisms (numerics tests): epilogue 0 store, 1 add, 2 y += alpha * row_scale * Wx, 3 SiLU gate, 4 GELU gate */
+void nt_b200_gemv_dense(float* y0, float* y1, float* y2, const void* W0, const void* W1, const void* W2, int out0, int out1, int out2, int n_mat, int K,
+                        const float* x, int dtype, int epilogue, const float* row_scale, float alpha, void* stream);
+void nt_b200_gemm_dense(float* C, const float* A, const void* W, int dtype, int T, int N, int K, int epilogue, const float* row_scale, float alpha, void* stream);
+void nt_b200_attention_window(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int heads, int kv_heads,
+                              int dim, int vdim, int window, int keep, float scale, float softcap, void* stream);
+void nt_b200_qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
+                              int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream);
+void nt_b200_glu_mul(float* out, const float* gate, const float* up, long long n, int gelu, void* stream);
+
 /* forward(tokens[seq_len], start_pos): logits of the last token. logits_host may be NULL.  Returns 0. */
 int  nt_model_forward(nt_model_t m, const int* tokens_host, int seq_len, int start_pos, float* logits_host);
 /* asynchronous launch only (no sync, no copy); nt_model_sync waits for the model's stream */

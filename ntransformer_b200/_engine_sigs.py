@@ -52,6 +52,16 @@ ENGINE_SIGNATURES = {
     "nt_tokenize": (_i, [C.c_char_p, C.c_char_p, _i, _vp, _i]),
     "nt_detokenize": (_i, [C.c_char_p, _vp, _i, _vp, _sz]),
     "nt_sample_token": (_i, [_vp, _i, _f, _i, _f, _f, _i, _vp, _i, C.c_uint64]),
+    "nt_model_load_dir": (_vp, [C.c_char_p, _i, _i]),
+    "nt_model_create_json": (_vp, [C.c_char_p, _i, _i]),
+    "nt_model_forward_logits": (_i, [_vp, _vp, _i, _i, _vp, _i, _vp]),
+    "nt_engine_load_path": (_i, [_vp, C.c_char_p, _i, _i]),
+    "nt_engine_generate_ids": (_i, [_vp, _vp, _i, _i, _f, _i, _f, _f, C.c_ulonglong, _vp, _i]),
+    "nt_b200_gemv_dense": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _f, _vp]),
+    "nt_b200_gemm_dense": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
+    "nt_b200_attention_window": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
+    "nt_b200_qk_norm_kv_write": (None, [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "nt_b200_glu_mul": (None, [_vp, _vp, _vp, C.c_longlong, _i, _vp]),
     "nt_tp_unique_id": (_i, [_vp]),
     "nt_tp_init": (_i, [_vp, _vp, _i, _i]),
 }

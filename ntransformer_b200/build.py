@@ -21,6 +21,8 @@ CLI = PKG / "ntransformer"
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function",
           "-ccbin", shutil.which("g++") or "g++"]
+# Kernels whose 32-bit mode must be exact to rounding (tanh / exp / division at full precision): no --use_fast_math.
+PRECISE = {"dense.cu", "attention_window.cu"}
 
 
 def _nvcc() -> str:
@@ -47,7 +49,8 @@ def _compile(src: Path, hdr_m: float, verbose: bool) -> Path:
     obj = OBJ / (src.relative_to(CSRC).as_posix().replace("/", "__") + ".o")
     if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_m):
         return obj
-    cmd = [_nvcc(), *ARCH, *COMMON, "-I", str(CSRC), "-I", str(PKG.parent / "include"), "-x", "cu", "-c", str(src), "-o", str(obj)]
+    flags = [f for f in COMMON if not (src.name in PRECISE and f == "--use_fast_math")]
+    cmd = [_nvcc(), *ARCH, *flags, "-I", str(CSRC), "-I", str(PKG.parent / "include"), "-x", "cu", "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)

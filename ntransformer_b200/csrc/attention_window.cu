@@ -1,0 +1,162 @@
+// attention_window.cu — attention over a sliding window plus the sequence's first `keep` tokens, scores soft-capped, no positional
+// rotation:   s_ij = cap * tanh(scale * <q_i, k_j> / cap)   (cap == 0: s_ij = scale * <q_i, k_j>),
+//             j visible from i  <=>  j <= i  and  (i - j < window  or  j < keep)        (window == 0: every j <= i),
+//             out_i = sum_j softmax_j(s_ij) v_j.
+// Query/key heads are `dim` wide, value heads `vdim` wide (they may differ); query head h reads key/value head h / (heads / kv_heads).
+// Keys and values come from the per-layer cache ([max_seq, kv_heads * dim] and [max_seq, kv_heads * vdim], F32 or BF16 storage):
+// the caller writes the step's rows first (qk_norm_kv_write), so a prompt portion, a whole prompt and a decoded token all take the
+// same kernel and see the same stored values.  Softmax, score and the weighted sum are F32.
+//   one CTA per (query token, head); its warps stride over the visible keys (the kept prefix, then the window) with a running
+//   (max, sum, acc) each, merged through shared memory at the end.
+// Compiled WITHOUT --use_fast_math (tanhf / expf at full precision).
+#include "kernels_internal.h"
+#include "ring.cuh"
+#include <cuda_bf16.h>
+#include <cfloat>
+
+namespace nt { namespace b200 {
+
+namespace {
+
+constexpr int AW_WARPS = 4;
+constexpr int AW_MAXV = 8;      // value elements per lane: vdim <= 256
+
+__device__ __forceinline__ float cache_ld(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float cache_ld(const __nv_bfloat16* p, size_t i) { return __uint_as_float((unsigned)reinterpret_cast<const unsigned short*>(p)[i] << 16); }
+__device__ __forceinline__ void cache_st(float* p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void cache_st(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+template <typename KT>
+__global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* __restrict__ out, const float* __restrict__ Q, const KT* __restrict__ kc,
+                                                                         const KT* __restrict__ vc, const int* __restrict__ pos_dev, int p0,
+                                                                         WindowAttn a) {
+    extern __shared__ float sm[];                 // q[dim] | per-warp acc[AW_WARPS][vdim] | m[AW_WARPS] | l[AW_WARPS]
+    float* qs = sm;
+    float* accs = sm + a.dim;
+    float* ms = accs + AW_WARPS * a.vdim;
+    float* ls = ms + AW_WARPS;
+    const int t = blockIdx.x, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pos = (pos_dev ? *pos_dev : p0) + t;
+    const float* q = Q + (size_t)t * a.heads * a.dim + (size_t)h * a.dim;
+    for (int i = threadIdx.x; i < a.dim; i += AW_WARPS * 32) qs[i] = q[i];
+    __syncthreads();
+    // visible keys: [0, n_first) and [lo, pos]
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int n_first = min(a.keep, lo);
+    const int n_keys = n_first + (pos - lo + 1);
+    const size_t kstride = (size_t)a.kv_heads * a.dim, vstride = (size_t)a.kv_heads * a.vdim;
+    float m = -FLT_MAX, l = 0.f, acc[AW_MAXV];
+#pragma unroll
+    for (int e = 0; e < AW_MAXV; e++) acc[e] = 0.f;
+    for (int n = warp; n < n_keys; n += AW_WARPS) {
+        const int j = n < n_first ? n : lo + (n - n_first);
+        const KT* kr = kc + (size_t)j * kstride + (size_t)g * a.dim;
+        float d = 0.f;
+        for (int i = lane; i < a.dim; i += 32) d = fmaf(qs[i], cache_ld(kr, i), d);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
+        float sc = d * a.scale;
+        if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+        const float mn = fmaxf(m, sc);
+        const float corr = expf(m - mn), p = expf(sc - mn);
+        l = l * corr + p;
+        const KT* vr = vc + (size_t)j * vstride + (size_t)g * a.vdim;
+#pragma unroll
+        for (int e = 0; e < AW_MAXV; e++) {
+            const int i = lane + 32 * e;
+            if (i < a.vdim) acc[e] = fmaf(p, cache_ld(vr, i), acc[e] * corr);
+        }
+        m = mn;
+    }
+    if (lane == 0) { ms[warp] = m; ls[warp] = l; }
+#pragma unroll
+    for (int e = 0; e < AW_MAXV; e++) { const int i = lane + 32 * e; if (i < a.vdim) accs[warp * a.vdim + i] = acc[e]; }
+    __syncthreads();
+    float M = -FLT_MAX;
+    for (int w = 0; w < AW_WARPS; w++) M = fmaxf(M, ms[w]);
+    float L = 0.f;
+    for (int w = 0; w < AW_WARPS; w++) L += ls[w] * expf(ms[w] - M);
+    float* o = out + (size_t)t * a.heads * a.vdim + (size_t)h * a.vdim;
+    for (int i = threadIdx.x; i < a.vdim; i += AW_WARPS * 32) {
+        float v = 0.f;
+        for (int w = 0; w < AW_WARPS; w++) v += accs[w * a.vdim + i] * expf(ms[w] - M);
+        o[i] = v / L;
+    }
+}
+
+// grid (tokens, 2).  y == 0: the query row, RMS-normalised over its whole length in place (or left alone);
+// y == 1: the key row, normalised the same way, and the value row, both written to cache row pos.
+template <typename KT>
+__global__ void __launch_bounds__(256) qk_norm_kv_write_kernel(float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                                                               const float* __restrict__ qn, const float* __restrict__ kn, float eps, KT* __restrict__ kc,
+                                                               KT* __restrict__ vc, const int* __restrict__ pos_dev, int p0, int qdim, int kdim, int vdim) {
+    __shared__ float red[8];
+    __shared__ float inv_s;
+    const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pos = (pos_dev ? *pos_dev : p0) + t;
+    const bool is_q = blockIdx.y == 0;
+    const int n = is_q ? qdim : kdim;
+    const float* src = is_q ? Q + (size_t)t * qdim : K + (size_t)t * kdim;
+    const float* gain = is_q ? qn : kn;
+    float inv = 1.f;
+    if (gain) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < n; i += 256) ss = fmaf(src[i], src[i], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float tot = 0.f;
+            for (int w = 0; w < 8; w++) tot += red[w];
+            inv_s = 1.0f / sqrtf(tot / (float)n + eps);
+        }
+        __syncthreads();
+        inv = inv_s;
+    }
+    if (is_q) {
+        if (gain) { float* qr = Q + (size_t)t * qdim; for (int i = threadIdx.x; i < n; i += 256) qr[i] = qr[i] * inv * gain[i]; }
+        return;
+    }
+    for (int i = threadIdx.x; i < kdim; i += 256) cache_st(kc, (size_t)pos * kdim + i, gain ? src[i] * inv * gain[i] : src[i]);
+    const float* vr = V + (size_t)t * vdim;
+    for (int i = threadIdx.x; i < vdim; i += 256) cache_st(vc, (size_t)pos * vdim + i, vr[i]);
+}
+
+}  // namespace
+
+void attention_window(float* out, const float* Q, const void* kc, const void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0,
+                      const WindowAttn& a, cudaStream_t s) {
+    NT_CHECK(a.vdim <= 32 * AW_MAXV, "attention_window: value heads wider than 256 are not covered");
+    NT_CHECK(a.heads % a.kv_heads == 0, "attention_window: heads must be a multiple of kv_heads");
+    NT_CHECK(cache_dt == DType::F32 || cache_dt == DType::BF16, "attention_window: F32 or BF16 cache");
+    if (tokens <= 0) return;
+    const size_t smem = sizeof(float) * ((size_t)a.dim + (size_t)AW_WARPS * a.vdim + 2 * AW_WARPS);
+    if (cache_dt == DType::F32)
+        launch_k(attention_window_kernel<float>, dim3(tokens, a.heads), dim3(AW_WARPS * 32), smem, s, out, Q, static_cast<const float*>(kc),
+                 static_cast<const float*>(vc), pos_dev, p0, a);
+    else
+        launch_k(attention_window_kernel<__nv_bfloat16>, dim3(tokens, a.heads), dim3(AW_WARPS * 32), smem, s, out, Q,
+                 static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), pos_dev, p0, a);
+    count_launch();
+}
+
+void qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
+                      DType cache_dt, int tokens, const int* pos_dev, int p0, int qdim, int kdim, int vdim, cudaStream_t s) {
+    NT_CHECK(cache_dt == DType::F32 || cache_dt == DType::BF16, "qk_norm_kv_write: F32 or BF16 cache");
+    if (tokens <= 0) return;
+    if (cache_dt == DType::F32)
+        launch_k(qk_norm_kv_write_kernel<float>, dim3(tokens, 2), dim3(256), 0, s, Q, K, V, q_gain, k_gain, eps, static_cast<float*>(kc),
+                 static_cast<float*>(vc), pos_dev, p0, qdim, kdim, vdim);
+    else
+        launch_k(qk_norm_kv_write_kernel<__nv_bfloat16>, dim3(tokens, 2), dim3(256), 0, s, Q, K, V, q_gain, k_gain, eps,
+                 static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), pos_dev, p0, qdim, kdim, vdim);
+    count_launch();
+}
+
+}}  // namespace nt::b200

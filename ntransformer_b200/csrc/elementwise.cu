@@ -239,6 +239,7 @@ __device__ float dequant_at(const uint8_t* row, int dt, int i) {
     switch (dt) {
         case (int)DType::F32: return reinterpret_cast<const float*>(row)[i];
         case (int)DType::F16: return h2f(reinterpret_cast<const uint16_t*>(row)[i]);
+        case (int)DType::BF16: return __uint_as_float((unsigned)reinterpret_cast<const uint16_t*>(row)[i] << 16);
         case (int)DType::Q8_0: {
             const uint8_t* b = row + (size_t)(i >> 5) * 34;
             return h2f(*reinterpret_cast<const uint16_t*>(b)) * (float)(int8_t)b[2 + (i & 31)];

@@ -3,6 +3,8 @@
 #include "../../../include/nt_b200_engine.h"
 #include "engine.h"
 #include "tp_comm.h"
+#include "json.h"
+#include "model_registry.h"
 #include <cstring>
 #include <algorithm>
 #include <memory>
@@ -54,6 +56,73 @@ nt_model_t nt_model_create(const nt_model_config* c, int tp_rank, int tp_size) {
     auto* h = new ModelHandle();
     h->model.init(cfg, tp_rank, tp_size);
     return h;
+}
+nt_model_t nt_model_load_dir(const char* dir, int max_context, int exact_f32) {
+    auto* h = new ModelHandle();
+    h->model.set_exact_f32(exact_f32 != 0);
+    if (!dir || !h->model.load_dir(dir, max_context)) { delete h; return nullptr; }
+    return h;
+}
+nt_model_t nt_model_create_json(const char* config_json, int max_context, int exact_f32) {
+    if (!config_json) return nullptr;
+    Json root;
+    std::string err;
+    if (!Json::parse(std::string(config_json), root, &err) || !root.is_object()) { fprintf(stderr, "nt_model_create_json: %s\n", err.c_str()); return nullptr; }
+    const ModelFamily* f = find_model_family(root.at("architecture").string_or(""));
+    ModelConfig cfg;
+    if (!f) { fprintf(stderr, "nt_model_create_json: unregistered architecture\n"); return nullptr; }
+    cfg.architecture = f->architecture;
+    if (!f->config_from_json(root, cfg, err)) { fprintf(stderr, "nt_model_create_json: %s\n", err.c_str()); return nullptr; }
+    cfg.max_seq_len = std::max(1, max_context);
+    auto* h = new ModelHandle();
+    h->model.set_exact_f32(exact_f32 != 0);
+    h->model.init(cfg, 0, 1);
+    return h;
+}
+int nt_model_forward_logits(nt_model_t m, const int* tokens, int n, int start_pos, const int* want, int n_want, float* logits_host) {
+    if (!m || !tokens || n < 1 || n_want < 0 || (n_want > 0 && (!want || !logits_host))) return -1;
+    H(m)->model.forward_logits(tokens, n, start_pos, want, n_want, logits_host);
+    return 0;
+}
+int nt_engine_load_path(nt_engine_t e, const char* path, int max_context, int exact_f32) {
+    if (!e || !path) return -1;
+    Engine* en = static_cast<Engine*>(e);
+    en->model().set_exact_f32(exact_f32 != 0);
+    return en->load(path, max_context) ? 0 : -1;
+}
+int nt_engine_generate_ids(nt_engine_t e, const int* prompt_ids, int n_prompt, int max_tokens, float temperature, int top_k, float top_p,
+                           float repeat_penalty, unsigned long long seed, int* out_ids, int cap) {
+    if (!e || !prompt_ids || n_prompt < 1) return -1;
+    GenerateConfig cfg;
+    cfg.max_tokens = max_tokens; cfg.temperature = temperature; cfg.top_k = top_k; cfg.top_p = top_p; cfg.repeat_penalty = repeat_penalty;
+    cfg.seed = seed; cfg.verbose = false;
+    const std::vector<int> ids = static_cast<Engine*>(e)->generate_ids(std::vector<int>(prompt_ids, prompt_ids + n_prompt), cfg);
+    for (int i = 0; i < (int)ids.size() && i < cap; i++) out_ids[i] = ids[(size_t)i];
+    return (int)ids.size();
+}
+// kernel-level entries of the layer-spec mechanisms (csrc/dense.cu, csrc/attention_window.cu) for numerics tests
+void nt_b200_gemv_dense(float* y0, float* y1, float* y2, const void* W0, const void* W1, const void* W2, int out0, int out1, int out2, int n_mat, int K,
+                        const float* x, int dtype, int epilogue, const float* row_scale, float alpha, void* stream) {
+    GemvMat m[3];
+    const void* Ws[3] = {W0, W1, W2}; float* ys[3] = {y0, y1, y2}; const int outs[3] = {out0, out1, out2};
+    for (int i = 0; i < 3; i++) { m[i].W = Ws[i]; m[i].y = ys[i]; m[i].out = outs[i]; m[i].dtype = (nt::DType)dtype; }
+    gemv_dense(m, n_mat, K, x, (DenseEpilogue)epilogue, row_scale, alpha, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_gemm_dense(float* Cm, const float* A, const void* W, int dtype, int T, int N, int K, int epilogue, const float* row_scale, float alpha, void* stream) {
+    gemm_dense(Cm, A, W, (nt::DType)dtype, 0, T, N, K, (DenseEpilogue)epilogue, row_scale, alpha, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_attention_window(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int heads, int kv_heads,
+                              int dim, int vdim, int window, int keep, float scale, float softcap, void* stream) {
+    WindowAttn a;
+    a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.window = window; a.keep = keep; a.scale = scale; a.softcap = softcap;
+    attention_window(out, Q, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, a, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
+                              int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream) {
+    qk_norm_kv_write(Q, K, V, q_gain, k_gain, eps, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, qdim, kdim, vdim, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_glu_mul(float* out, const float* gate, const float* up, long long n, int gelu, void* stream) {
+    glu_mul(out, gate, up, (size_t)n, gelu != 0, static_cast<cudaStream_t>(stream));
 }
 int nt_model_set_tensor(nt_model_t m, const char* name, const void* p, int dtype, size_t pitch) {
     return (m && name && H(m)->model.set_tensor(name, p, (nt::DType)dtype, pitch)) ? 0 : -1;

@@ -9,7 +9,7 @@ using Clock = std::chrono::steady_clock;
 static float ms_since(Clock::time_point t0) { return std::chrono::duration<float, std::milli>(Clock::now() - t0).count(); }
 
 bool Engine::load(const std::string& path, int max_context) {
-    if (!model_.load_gguf(path, max_context)) return false;
+    if (!model_.load(path, max_context)) return false;          // a GGUF file or a model folder (engine/model_registry.h)
     tok_.init(model_.vocab(), model_.config().bos_token_id, model_.config().eos_token_id);
     return true;
 }
@@ -37,6 +37,21 @@ bool Engine::load_tp(const std::string& path, int max_context, int tp_rank, int 
 }
 
 std::string Engine::generate(const std::string& prompt, const GenerateConfig& cfg, TokenCallback cb) {
+    std::string out;
+    generate_ids(tok_.encode(prompt, true), cfg, [&](int id) {
+        const std::string piece = tok_.decode_token(id);
+        out += piece;
+        if (cb) return cb(piece, id);
+        if (cfg.verbose) { fputs(piece.c_str(), stdout); fflush(stdout); }
+        return true;
+    });
+    if (cfg.verbose) { fputc('\n', stdout); print_stats(stats_); }
+    return out;
+}
+
+// Generation over token ids: prompt pass, then one step per sampled token (GPU argmax / GPU sampler / host sampler).  Families
+// without a vocabulary (model folders) are driven through this entry; the text form above wraps it.
+std::vector<int> Engine::generate_ids(const std::vector<int>& prompt_ids, const GenerateConfig& cfg, const std::function<bool(int)>& on_token) {
     Stats st;
     Sampler sampler;
     SamplerConfig sc;
@@ -44,14 +59,15 @@ std::string Engine::generate(const std::string& prompt, const GenerateConfig& cf
     sc.repeat_penalty = cfg.repeat_penalty; sc.repeat_window = cfg.repeat_window; sc.seed = cfg.seed;
     sampler.init(sc);
 
-    std::vector<int> tokens = tok_.encode(prompt, true);
+    std::vector<int> tokens = prompt_ids;
+    std::vector<int> produced;
     st.prompt_tokens = (int)tokens.size();
     if (cfg.verbose) fprintf(stderr, "Prompt tokens: %d\n", st.prompt_tokens);
-    if (st.prompt_tokens > model_.config().max_seq_len) {
+    if (st.prompt_tokens < 1 || st.prompt_tokens > model_.config().max_seq_len) {
         // the reference writes past its KV cache here (transformer.cpp:629-640 has no check); an error return instead of an abort
         fprintf(stderr, "Error: the prompt has %d tokens, the context holds %d (use --ctx-size)\n", st.prompt_tokens, model_.config().max_seq_len);
         stats_ = st;
-        return std::string();
+        return produced;
     }
     const int vocab = model_.config().vocab_size;
     std::vector<float> logits((size_t)vocab);
@@ -81,11 +97,8 @@ std::string Engine::generate(const std::string& prompt, const GenerateConfig& cf
     st.prefill_ms = ms_since(t0);
     int next = next_from(dl);
     tokens.push_back(next);
-    std::string out, piece = tok_.decode_token(next);
-    out += piece;
-    bool stop = false;
-    if (cb) stop = !cb(piece, next);
-    else if (cfg.verbose) { fputs(piece.c_str(), stdout); fflush(stdout); }
+    produced.push_back(next);
+    const bool stop = on_token && !on_token(next);
 
     if (!stop) {
         auto d0 = Clock::now();
@@ -96,17 +109,14 @@ std::string Engine::generate(const std::string& prompt, const GenerateConfig& cf
             dl = model_.forward(&next, 1, pos++);
             next = next_from(dl);
             tokens.push_back(next);
-            piece = tok_.decode_token(next);
-            out += piece;
+            produced.push_back(next);
             st.gen_tokens++;
-            if (cb) { if (!cb(piece, next)) break; }
-            else if (cfg.verbose) { fputs(piece.c_str(), stdout); fflush(stdout); }
+            if (on_token && !on_token(next)) break;
         }
         st.decode_ms = ms_since(d0);
     }
     stats_ = st;
-    if (cfg.verbose) { fputc('\n', stdout); print_stats(st); }
-    return out;
+    return produced;
 }
 
 void Engine::chat(const GenerateConfig& cfg) {

@@ -32,6 +32,10 @@ public:
     bool load_tp(const std::string& model_path, int max_context, int tp_rank, int tp_size, const void* nccl_id);
     int tp_rank() const { return tp_rank_; }
     std::string generate(const std::string& prompt, const GenerateConfig& cfg, TokenCallback cb = nullptr);
+    // The same loop over token ids (no tokenizer involved): returns the generated ids; on_token returning false stops.
+    std::vector<int> generate_ids(const std::vector<int>& prompt_ids, const GenerateConfig& cfg, const std::function<bool(int)>& on_token = nullptr);
+    // Replays a step trace (engine/trace.cpp): JSON lines on `in`, logits files into out_dir.  Returns the process exit code.
+    int replay_trace(FILE* in, const std::string& out_dir);
     void chat(const GenerateConfig& cfg);
     void benchmark(const std::string& prompt, int n_tokens);
     const ModelConfig& config() const { return model_.config(); }

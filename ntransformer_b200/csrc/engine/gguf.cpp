@@ -101,6 +101,11 @@ void ModelConfig::print() const {          // same lines as reference config.cpp
     fprintf(stderr, "RoPE theta: %.1f, GQA: %s (group=%d)\n", rope_theta, n_kv_heads < n_heads ? "yes" : "no",
             n_kv_heads ? n_heads / n_kv_heads : 0);
     fprintf(stderr, "BOS: %d, EOS: %d\n", bos_token_id, eos_token_id);
+    for (size_t i = 0; i < layers.size(); i++) {
+        const LayerSpec& L = layers[i];
+        fprintf(stderr, "  layer %zu: heads %d/%d, dim %d, vdim %d, window %d (+%d first), softcap %g, scale %g, ff %d%s\n", i, L.heads, L.kv_heads, L.dim, L.vdim,
+                L.window, L.keep_first, L.softcap, L.scale, L.ff, L.weights_of >= 0 ? (" (weights of layer " + std::to_string(L.weights_of) + ")").c_str() : "");
+    }
 }
 
 GGUFFile::~GGUFFile() {

@@ -10,6 +10,7 @@
 #include <variant>
 #include <vector>
 #include "../nt_types.h"
+#include "layer_spec.h"
 
 namespace nt { namespace b200 {
 
@@ -22,6 +23,10 @@ struct ModelConfig {                       // reference src/model/config.h:16-58
     bool rope_interleaved = false;         // never set from GGUF by the reference
     int max_seq_len = 4096;
     int bos_token_id = 1, eos_token_id = 2;
+    // Families described layer by layer (a model folder, engine/model_registry.h): one entry per layer; empty for the GGUF Llama block.
+    std::vector<LayerSpec> layers;
+    float residual_mult = 1.0f;            // m of the PARALLEL block form
+    bool layer_spec() const { return !layers.empty(); }
     void print() const;
 };
 

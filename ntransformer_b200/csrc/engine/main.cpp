@@ -15,7 +15,12 @@ using namespace nt::b200;
 
 static void usage(const char* prog) {
     fprintf(stderr, "NTransformer (B200 resident engine)\n\nUsage: %s [options] -m <model.gguf>\n\nOptions:\n", prog);
-    fprintf(stderr, "  -m, --model <path>       Path to GGUF model file (required)\n");
+    fprintf(stderr, "  -m, --model <path>       Path to a GGUF model file, or to a model folder (config.json + model.safetensors) (required)\n");
+    fprintf(stderr, "  --ids <\"i j k\">         Prompt as token ids (models without a vocabulary); generated ids are printed\n");
+    fprintf(stderr, "  --dtype <name>           Model folders: bfloat16 (default: weights as stored, BF16 cache) or float32 (everything in true 32-bit)\n");
+    fprintf(stderr, "  --trace <out dir>        Replay a step trace from standard input (JSON lines: step, entries[id, tokens, want], end) and write\n"
+                    "                           the wanted logits as <out dir>/<step>.f32; prints \"done <step>\" after each step\n");
+    fprintf(stderr, "  --max-tokens <int>       Same as --ctx-size\n");
     fprintf(stderr, "  -p, --prompt <text>      Prompt text (default: interactive mode)\n");
     fprintf(stderr, "  -n, --n-tokens <int>     Max tokens to generate (default: 256)\n");
     fprintf(stderr, "  -t, --temperature <float> Temperature (default: 0.7)\n");
@@ -40,7 +45,7 @@ static void usage(const char* prog) {
 }
 
 int main(int argc, char** argv) {
-    std::string model_path, prompt;
+    std::string model_path, prompt, trace_out, ids_text, dtype = "bfloat16";
     int max_context = 4096, tp = 1, device = 0;
     bool bench = false, chat = false;
     GenerateConfig cfg;
@@ -58,6 +63,10 @@ int main(int argc, char** argv) {
         else if (a == "--repeat-penalty") { if (auto v = val()) cfg.repeat_penalty = std::stof(v); }
         else if (a == "--seed") { if (auto v = val()) cfg.seed = std::stoull(v); }
         else if (a == "-c" || a == "--ctx-size") { if (auto v = val()) max_context = std::stoi(v); }
+        else if (a == "--max-tokens") { if (auto v = val()) max_context = std::stoi(v); }
+        else if (a == "--trace" || a == "--out") { if (auto v = val()) trace_out = v; }
+        else if (a == "--ids") { if (auto v = val()) ids_text = v; }
+        else if (a == "--dtype") { if (auto v = val()) dtype = v; }
         else if (a == "--tp") { if (auto v = val()) tp = std::stoi(v); }
         else if (a == "--device") { if (auto v = val()) device = std::stoi(v); }
         else if (a == "--gpu-sampler") cfg.gpu_sampler = true;
@@ -74,6 +83,8 @@ int main(int argc, char** argv) {
         } else { fprintf(stderr, "Unknown option: %s\n", a.c_str()); usage(argv[0]); return 1; }
     }
     if (model_path.empty()) { fprintf(stderr, "Error: model path required (-m)\n\n"); usage(argv[0]); return 1; }
+    if (dtype != "bfloat16" && dtype != "float32") { fprintf(stderr, "Error: --dtype must be bfloat16 or float32\n"); return 1; }
+    if (!trace_out.empty() && tp != 1) { fprintf(stderr, "Error: --trace runs on one GPU\n"); return 1; }
     if (tp < 1 || tp > 8 || (tp & (tp - 1))) { fprintf(stderr, "Error: --tp must be 1, 2, 4 or 8\n"); return 1; }
     // Tensor parallel: one process per GPU.  The ranks are forked here, BEFORE anything touches CUDA; rank 0 hands the NCCL id to
     // the others through a shared page.  All ranks run the same generation with the same seed (bit-identical logits everywhere).
@@ -82,7 +93,7 @@ int main(int argc, char** argv) {
     int rank = 0;
     std::vector<pid_t> kids;
     if (tp > 1) {
-        if (chat || (prompt.empty() && !bench)) { fprintf(stderr, "Error: --tp needs -p <prompt> or --benchmark (the ranks cannot share an interactive stdin)\n"); return 1; }
+        if (chat || (prompt.empty() && !bench && ids_text.empty())) { fprintf(stderr, "Error: --tp needs -p <prompt> or --benchmark (the ranks cannot share an interactive stdin)\n"); return 1; }
         sh = static_cast<Shared*>(mmap(nullptr, sizeof(Shared), PROT_READ | PROT_WRITE, MAP_SHARED | MAP_ANONYMOUS, -1, 0));
         if (sh == MAP_FAILED) { perror("mmap"); return 1; }
         new (&sh->ready) std::atomic<int>(0);
@@ -97,6 +108,7 @@ int main(int argc, char** argv) {
     int rc = 0;
     {
         Engine engine;
+        engine.model().set_exact_f32(dtype == "float32");
         bool ok;
         if (tp > 1) {
             if (rank == 0) {
@@ -114,6 +126,15 @@ int main(int argc, char** argv) {
             ok = engine.load(model_path, max_context);
         }
         if (!ok) { fprintf(stderr, "Failed to load model: %s\n", model_path.c_str()); rc = 1; }
+        else if (!trace_out.empty()) rc = engine.replay_trace(stdin, trace_out);
+        else if (!ids_text.empty()) {
+            std::vector<int> ids;
+            for (const char* p = ids_text.c_str(); *p;) { char* e = nullptr; long v = strtol(p, &e, 10); if (e == p) { p++; continue; } ids.push_back((int)v); p = e; }
+            for (int id : ids) if (id < 0 || id >= engine.config().vocab_size) { fprintf(stderr, "Error: token id %d is outside the vocabulary\n", id); return 1; }
+            cfg.verbose = false;
+            engine.generate_ids(ids, cfg, [](int id) { printf("%d ", id); fflush(stdout); return true; });
+            printf("\n");
+        }
         else if (bench) engine.benchmark(prompt.empty() ? "The meaning of life is" : prompt, cfg.max_tokens);
         else if (chat || prompt.empty()) engine.chat(cfg);
         else engine.generate(prompt, cfg);

@@ -74,6 +74,9 @@ Model::~Model() {
     for (void* p : {(void*)pf_.x, (void*)pf_.q, (void*)pf_.k, (void*)pf_.v, (void*)pf_.attn, pf_.ws, pf_.ws2, (void*)pf_.tok, (void*)pf_.pos,
                     (void*)pf_.g, (void*)pf_.u, pf_.whi, pf_.wlo})
         if (p) cudaFree(p);
+    for (void* p : kcs_) if (p) cudaFree(p);
+    for (void* p : vcs_) if (p) cudaFree(p);
+    for (void* p : {(void*)pf_.h, (void*)pf_.tmp, pf_.hws, (void*)want_out_}) if (p) cudaFree(p);
     if (argmax_host_) cudaFreeHost(argmax_host_);
     if (stream_) cudaStreamDestroy(stream_);
 }
@@ -88,6 +91,14 @@ void Model::init(const ModelConfig& cfg, int tp_rank, int tp_size) {
     tp_rank_ = tp_rank;
     tp_size_ = tp_size;
     NT_CHECK(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, "bad tensor-parallel rank/size");
+    if (cfg.layer_spec()) {
+        NT_CHECK(tp_size == 1, "layer-spec families run on one GPU");
+        family_ = find_model_family(cfg.architecture);
+        NT_CHECK(family_ != nullptr, "layer-spec configuration of an unregistered architecture");
+        nh_l_ = cfg.n_heads; nkv_l_ = cfg.n_kv_heads; inter_l_ = cfg.intermediate_size; vocab_l_ = cfg.vocab_size;
+        layers_.assign((size_t)cfg.n_layers, LayerWeights{});
+        return;
+    }
     NT_CHECK(cfg.n_heads % tp_size == 0 && cfg.n_kv_heads % tp_size == 0, "heads must divide by tp_size");
     NT_CHECK(cfg.intermediate_size % tp_size == 0, "intermediate_size must divide by tp_size");
     nh_l_ = cfg.n_heads / tp_size;
@@ -98,6 +109,11 @@ void Model::init(const ModelConfig& cfg, int tp_rank, int tp_size) {
 }
 
 bool Model::set_tensor(const std::string& name, const void* ptr, DType dt, size_t pitch) {
+    if (cfg_.layer_spec()) {
+        for (const TensorBinding& b : family_->tensors(cfg_))
+            if (b.name == name) return bind_slot(b.slot, b.layer, ptr, dt, b.rows, b.cols, pitch);
+        return false;
+    }
     const int hidden = cfg_.hidden_size, hd = cfg_.head_dim;
     auto W = [&](Weight& w, int rows, int cols) {
         w.ptr = ptr; w.dtype = dt; w.rows = rows; w.cols = cols;
@@ -334,6 +350,7 @@ bool Model::load_gguf(const std::string& path, int max_context, int tp_rank, int
 }
 
 bool Model::finalize() {
+    if (cfg_.layer_spec()) return finalize_spec();
     const int hidden = cfg_.hidden_size, hd = cfg_.head_dim;
     if (!embd_.ptr || !out_norm_) { fprintf(stderr, "model: token_embd / output_norm missing\n"); return false; }
     if (!head_.ptr) {
@@ -382,17 +399,39 @@ bool Model::finalize() {
 }
 
 void Model::clear_kv() {
+    if (cfg_.layer_spec()) {
+        for (int i = 0; i < cfg_.n_layers; i++) {
+            const LayerSpec& L = cfg_.layers[(size_t)i];
+            const size_t es = dtype_size(cache_dt_);
+            NT_CUDA_CHECK(cudaMemsetAsync(kcs_[(size_t)i], 0, es * cfg_.max_seq_len * L.kv_heads * L.dim, stream_));
+            NT_CUDA_CHECK(cudaMemsetAsync(vcs_[(size_t)i], 0, es * cfg_.max_seq_len * L.kv_heads * L.vdim, stream_));
+        }
+        return;
+    }
     const size_t kv_elems = (size_t)cfg_.n_layers * cfg_.max_seq_len * nkv_l_ * cfg_.head_dim;
     NT_CUDA_CHECK(cudaMemsetAsync(kc_, 0, kv_elems * 2, stream_));
     NT_CUDA_CHECK(cudaMemsetAsync(vc_, 0, kv_elems * 2, stream_));
 }
 
 size_t Model::weight_bytes() const {
+    if (cfg_.layer_spec()) {          // every layer RUN reads its tensors, shared or not
+        size_t b = head_.bytes() + (size_t)cfg_.hidden_size * 4;
+        for (int i = 0; i < cfg_.n_layers; i++) {
+            const LayerWeights& L = layer_weights(i);
+            b += L.wq.bytes() + L.wk.bytes() + L.wv.bytes() + L.wo.bytes() + L.gate.bytes() + L.up.bytes() + L.down.bytes();
+        }
+        return b;
+    }
     size_t b = head_.bytes() + (size_t)(2 * cfg_.n_layers + 1) * cfg_.hidden_size * 4;
     for (const LayerWeights& L : layers_) b += L.wq.bytes() + L.wk.bytes() + L.wv.bytes() + L.wo.bytes() + L.gate.bytes() + L.up.bytes() + L.down.bytes();
     return b;
 }
 size_t Model::bytes_per_token(int ctx) const {
+    if (cfg_.layer_spec()) {
+        size_t b = weight_bytes();
+        for (const LayerSpec& L : cfg_.layers) b += (size_t)std::min(ctx, L.window + L.keep_first) * L.kv_heads * (L.dim + L.vdim) * dtype_size(cache_dt_);
+        return b;
+    }
     return weight_bytes() + (size_t)2 * cfg_.n_layers * ctx * nkv_l_ * cfg_.head_dim * 2;
 }
 
@@ -463,6 +502,7 @@ void Model::ensure_xchg() {
 }
 
 bool Model::chain_ok() const {
+    if (cfg_.layer_spec()) return false;
     if ((tp_size_ != 1 && !xchg_) || !(fuse_mask_ & 1)) return false;
     if (cfg_.hidden_size % 128 != 0 || inter_l_ % 128 != 0 || (nh_l_ * cfg_.head_dim) % 128 != 0) return false;
     auto kq = [&](const Weight& w, int K) {
@@ -489,6 +529,7 @@ bool Model::chain_ok() const {
 //     already in flight (gemv_kquant.cu); only the intermediate-sized activation vector keeps its own quantise launch;
 //   unfused — 8-10 launches per layer (tensor parallel, mixed dtypes, NT_B200_FUSE=0).
 void Model::step_body(cudaStream_t s) {
+    if (cfg_.layer_spec()) { step_body_spec(s); return; }
     const int hidden = cfg_.hidden_size, hd = cfg_.head_dim, max_seq = cfg_.max_seq_len;
     const float scale = 1.0f / sqrtf((float)hd);                         // attention.cpp:21
     const size_t kv_stride = (size_t)max_seq * nkv_l_ * hd;               // transformer.cpp:629
@@ -560,6 +601,7 @@ void Model::step_body(cudaStream_t s) {
 }
 
 void Model::step_head(cudaStream_t s, bool from_chain) {
+    if (cfg_.layer_spec()) { step_head_spec(s); return; }
     const Weight* ws[1] = {&head_};                                               // final norm fused: transformer.cpp:657-665
     if (from_chain) {
         GemvMat m; m.W = head_.ptr; m.y = tp_size_ == 1 ? logits_ : logits_l_; m.out = head_.rows; m.dtype = head_.dtype; m.row_pitch = head_.pitch;
@@ -656,7 +698,7 @@ void Model::run_step_mega(bool with_head) {
 void Model::run_step(bool with_head) {
     // NT_B200_MEGAKERNEL: unset -> the model's own setting (set_use_megakernel, off by default), "0" -> off, anything else -> on
     const char* mk = getenv("NT_B200_MEGAKERNEL");
-    const bool want_mega = mk ? env_on("NT_B200_MEGAKERNEL") : use_mega_;
+    const bool want_mega = !cfg_.layer_spec() && (mk ? env_on("NT_B200_MEGAKERNEL") : use_mega_);
     if (want_mega && ensure_mega()) { run_step_mega(with_head); return; }
     ensure_xchg();
     if (!use_graph_ || getenv("NT_B200_NO_GRAPH")) {
@@ -782,9 +824,22 @@ void Model::prefill_batched(const int* tokens, int seq_len, int start_pos) {
             }
             prefill_gemm(pf_.x, pf_.ws2, L.down, T, true, s);
         }
+        if (!want_.empty()) emit_wanted(pf_.x, c0, T, s);
     }
     copy(hidden_, pf_.x + (size_t)(last_rows - 1) * hidden, hidden, s);       // last token's residual stream -> LM head
     step_head(s);
+}
+
+// Places of the current forward whose logits are collected (forward_logits); empty: only the last token's, in logits_.
+void Model::emit_wanted(const float* x_rows, int c0, int T, cudaStream_t s) {
+    const size_t vocab = (size_t)cfg_.vocab_size;
+    for (size_t w = 0; w < want_.size(); w++) {
+        const int t = want_[w];
+        if (t < c0 || t >= c0 + T) continue;
+        copy(hidden_, x_rows + (size_t)(t - c0) * cfg_.hidden_size, cfg_.hidden_size, s);
+        step_head(s);
+        NT_CUDA_CHECK(cudaMemcpyAsync(want_out_ + w * vocab, logits_, vocab * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    }
 }
 
 void Model::forward_async(const int* tokens, int seq_len, int start_pos) {
@@ -792,14 +847,37 @@ void Model::forward_async(const int* tokens, int seq_len, int start_pos) {
     NT_CHECK(seq_len >= 1, "forward: empty token list");
     NT_CHECK(start_pos >= 0 && start_pos + seq_len <= cfg_.max_seq_len, "forward: position beyond the KV cache (max_seq_len)");
     for (int t = 0; t < seq_len; t++) NT_CHECK(tokens[t] >= 0 && tokens[t] < cfg_.vocab_size, "token id out of range");
-    if (batched_prefill_ok(seq_len, start_pos)) { prefill_batched(tokens, seq_len, start_pos); return; }
+    if (cfg_.layer_spec()) {
+        if (prefill_min_tokens_ > 0 && seq_len >= prefill_min_tokens_ && !getenv("NT_B200_NO_BATCHED_PREFILL")) { prefill_spec(tokens, seq_len, start_pos); return; }
+    } else if (batched_prefill_ok(seq_len, start_pos)) { prefill_batched(tokens, seq_len, start_pos); return; }
+    size_t w = 0;
     for (int t = 0; t < seq_len; t++) {
         int tok = tokens[t];
-        NT_CHECK(tok >= 0 && tok < cfg_.vocab_size, "token id out of range");
         set_step_kernel<<<1, 1, 0, stream_>>>(step_dev_, tok, start_pos + t);
         count_launch();
-        run_step(t == seq_len - 1);
+        while (w < want_.size() && want_[w] < t) w++;
+        const bool wanted = w < want_.size() && want_[w] == t;
+        run_step(wanted || t == seq_len - 1);
+        if (wanted)
+            NT_CUDA_CHECK(cudaMemcpyAsync(want_out_ + w * (size_t)cfg_.vocab_size, logits_, (size_t)cfg_.vocab_size * sizeof(float),
+                                          cudaMemcpyDeviceToDevice, stream_));
     }
+}
+
+void Model::forward_logits(const int* tokens, int seq_len, int start_pos, const int* want, int n_want, float* out_host) {
+    NT_CHECK(tp_size_ == 1, "forward_logits: one GPU");
+    want_.assign(want, want + n_want);
+    for (int i = 0; i < n_want; i++) NT_CHECK(want[i] >= 0 && want[i] < seq_len && (i == 0 || want[i] > want[i - 1]), "forward_logits: wanted places must ascend inside the tokens");
+    if ((size_t)n_want > want_cap_) {
+        if (want_out_) { NT_CUDA_CHECK(cudaStreamSynchronize(stream_)); NT_CUDA_CHECK(cudaFree(want_out_)); }
+        want_cap_ = std::max<size_t>(64, (size_t)n_want);
+        want_out_ = dmalloc<float>(want_cap_ * (size_t)cfg_.vocab_size);
+    }
+    forward_async(tokens, seq_len, start_pos);
+    want_.clear();
+    if (n_want > 0)
+        NT_CUDA_CHECK(cudaMemcpyAsync(out_host, want_out_, (size_t)n_want * cfg_.vocab_size * sizeof(float), cudaMemcpyDeviceToHost, stream_));
+    NT_CUDA_CHECK((cudaError_t)sync());
 }
 
 int Model::sync() {

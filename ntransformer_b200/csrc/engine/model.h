@@ -16,6 +16,7 @@
 #include "gguf.h"
 #include "decode_mega.h"
 #include "peer_xchg.h"
+#include "model_registry.h"
 
 namespace nt { namespace b200 {
 
@@ -34,6 +35,11 @@ struct LayerWeights {
     const float* attn_norm = nullptr;
     const float* ffn_norm = nullptr;
     Weight wq, wk, wv, wo, gate, up, down;
+    // layer-spec families (engine/layer_spec.h): whole-projection query / key norm gains, per-channel branch gains (F32, may be null)
+    const float* q_norm = nullptr;
+    const float* k_norm = nullptr;
+    const float* ls1 = nullptr;
+    const float* ls2 = nullptr;
 };
 
 class Model {
@@ -45,6 +51,14 @@ public:
 
     // (a) from a GGUF file: parse, shard for (tp_rank, tp_size), upload, allocate, capture.
     bool load_gguf(const std::string& path, int max_context, int tp_rank = 0, int tp_size = 1);
+    // (a') from a model folder (config.json + model.safetensors) of a registered layer-spec family (engine/model_registry.h).
+    bool load_dir(const std::string& dir, int max_context);
+    // Either of the two, by what the path is (a directory or a file).
+    bool load(const std::string& path, int max_context);
+    // Layer-spec families, before load / finalize: keep every tensor, the KV cache and all arithmetic in true 32-bit (weights are
+    // widened once at load; prompt GEMMs run on CUDA cores).  Off: weights stay in their stored dtype (BF16), BF16 cache.
+    void set_exact_f32(bool on) { exact32_ = on; }
+    bool exact_f32() const { return exact32_; }
     // (b) from caller-owned device tensors (synthetic benchmarks): init -> set_tensor* -> finalize.
     void init(const ModelConfig& cfg, int tp_rank = 0, int tp_size = 1);
     bool set_tensor(const std::string& gguf_name, const void* dev_ptr, DType dtype, size_t row_pitch = 0);
@@ -55,6 +69,8 @@ public:
     // Runs seq_len tokens at positions start_pos.. and returns DEVICE logits [vocab] of the last token
     // (same contract as Transformer::forward, transformer.cpp:604-669; synchronises the stream).
     float* forward(const int* tokens, int seq_len, int start_pos);
+    // Like forward(), and also copies the logits at the wanted places (ascending indices into tokens) to out_host [n_want, vocab].
+    void forward_logits(const int* tokens, int seq_len, int start_pos, const int* want, int n_want, float* out_host);
     // Asynchronous variant used by the benchmark: no host sync.
     void forward_async(const int* tokens, int seq_len, int start_pos);
     // Greedy next token computed on the GPU from the last logits (argmax, lowest index on ties like Sampler::argmax).
@@ -93,6 +109,25 @@ public:
     int mega_plan_kinds(int* kinds, int cap);  // phase kinds of the per-token program; returns their number (0 when inactive)
 
 private:
+    // ---- layer-spec families (engine/model_spec.cu) ----
+    const LayerWeights& layer_weights(int i) const { const int j = cfg_.layer_spec() ? cfg_.layers[(size_t)i].weights_of : -1; return layers_[(size_t)(j >= 0 ? j : i)]; }
+    bool bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch);
+    bool finalize_spec();
+    void step_body_spec(cudaStream_t s);
+    void step_head_spec(cudaStream_t s);
+    void prefill_spec(const int* tokens, int seq_len, int start_pos);
+    void ensure_prefill_buffers_spec(int tokens);
+    bool spec_tc_ok(const Weight& w) const;
+    void spec_gemm(float* C, const float* A, const void* A_split, const Weight& w, int T, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s);
+    void emit_wanted(const float* x_rows, int c0, int T, cudaStream_t s);   // logits of the wanted places inside tokens [c0, c0 + T)
+    const ModelFamily* family_ = nullptr;
+    bool exact32_ = false;
+    DType cache_dt_ = DType::F16;
+    std::vector<void*> kcs_, vcs_;        // per-layer caches [max_seq, kv_heads * dim] / [max_seq, kv_heads * vdim] of cache_dt_
+    std::vector<int> want_;               // places (indices into the current forward's tokens) whose logits are collected
+    float* want_out_ = nullptr;           // device [want_cap_, vocab]
+    size_t want_cap_ = 0;
+
     bool ensure_mega();
     void run_step_mega(bool with_head);
     void step_body(cudaStream_t s);      // embedding + all layers for the token/position in step_dev_
@@ -145,6 +180,8 @@ private:
         float *g = nullptr, *u = nullptr;     // gate / up activations (only when those weights are not F16: unfused SwiGLU)
         void *whi = nullptr, *wlo = nullptr;  // dequantised weight matrix as an F16 hi/lo pair (quantised models)
         int *tok = nullptr, *pos = nullptr;
+        float *h = nullptr, *tmp = nullptr;   // layer-spec families: the block's normed input (read by both branches), a GEMM result before its scaled add
+        void *hws = nullptr;                  // ... and its F16 hi/lo split
     } pf_;
     // Prompts shorter than this replay token by token through the decode chain (exact-integer GEMVs); longer ones take the batched
     // tensor-core prefill, whose F32 accumulation inside the tensor cores truncates once per 16-deep MMA step: ~1e-5..1e-4 per GEMM,

@@ -1,0 +1,35 @@
+// model_registry.h — model families that load from a folder (config.json + model.safetensors).  A family is chosen by the
+// config's "architecture" string; it turns the JSON into a ModelConfig with one LayerSpec per layer and lists the tensors the
+// model needs, each bound to a slot of the resident model (engine/model.h).  The GGUF Llama family keeps its own loader
+// (Model::load_gguf); Model::load picks by what the path is.
+#pragma once
+#include <string>
+#include <vector>
+#include "gguf.h"
+#include "json.h"
+
+namespace nt { namespace b200 {
+
+enum class TensorSlot { EMBED, HEAD, OUT_NORM, NORM1, NORM2, WQ, WK, WV, WO, Q_NORM, K_NORM, GATE, UP, DOWN, LS1, LS2 };
+
+struct TensorBinding {
+    std::string name;      // in the checkpoint
+    TensorSlot slot;
+    int layer;             // -1 for model-level tensors
+    int rows, cols;        // expected shape (vectors: rows == 1)
+};
+
+struct ModelFamily {
+    const char* architecture;
+    bool (*config_from_json)(const Json& root, ModelConfig& cfg, std::string& err);
+    std::vector<TensorBinding> (*tensors)(const ModelConfig& cfg);
+};
+
+const ModelFamily* find_model_family(const std::string& architecture);
+const std::vector<const ModelFamily*>& model_families();
+// Reads <dir>/config.json; false (+ message) when it is missing, malformed or names no registered family.
+bool read_model_dir(const std::string& dir, ModelConfig& cfg, const ModelFamily** family);
+
+const ModelFamily* zelunex_family();      // engine/zelunex.cpp
+
+}}  // namespace nt::b200

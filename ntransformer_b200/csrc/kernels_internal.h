@@ -127,6 +127,31 @@ bool sample_topk_supported(int n, float temperature, int top_k);
 bool sample_topk(float* logits_dev, int n, float temperature, int top_k, float top_p, float repeat_penalty, const int* recent_dev,
                  int n_recent, float r, int* out_dev, cudaStream_t s);
 
+// ---- dense.cu / attention_window.cu: kernels of the layer-spec model families (dense F32 / F16 / BF16 weights, F32 activations) ----
+enum DenseEpilogue { DENSE_STORE = 0, DENSE_ADD = 1, DENSE_SCALED_ADD = 2 /* y[r] += alpha * row_scale[r] * (W.x)[r]; row_scale may be null */,
+                     DENSE_SWIGLU = 3 /* y0 = silu(W0.x) * (W1.x) */, DENSE_GEGLU = 4 /* y0 = gelu_tanh(W0.x) * (W1.x) */ };
+bool dense_dtype(DType dt);
+// Up to 3 matrices of one dense dtype sharing the activation vector x[K] (GemvMat::y: each matrix's output rows).
+void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s);
+// C[T,N] (ep)= A[T,K] . W[N,K]^T in true FP32 on CUDA cores (store / add / scaled-add; row_scale indexes N).
+void gemm_dense(float* C, const float* A, const void* W, DType dt, size_t row_pitch, int T, int N, int K, DenseEpilogue ep,
+                const float* row_scale, float alpha, cudaStream_t s);
+void glu_mul(float* out, const float* gate, const float* up, size_t n, bool gelu, cudaStream_t s);      // out = act(gate) * up
+void scaled_add_rows(float* x, const float* y, const float* row_scale, float alpha, int rows, int cols, cudaStream_t s);   // x[r,c] += alpha * row_scale[c] * y[r,c]
+void dense_to_f32(float* out, const void* in, DType dt, size_t n, cudaStream_t s);
+struct WindowAttn {
+    int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
+    int window = 0, keep = 0;          // window == 0: full causal
+    float scale = 1.f, softcap = 0.f;  // softcap == 0: none
+};
+// Q [tokens, heads*dim] at positions base.. (base = *pos_dev when pos_dev is given, else p0); caches [max_seq, kv_heads*dim|vdim] of
+// cache_dt (F32 or BF16) that already hold the rows of these tokens; out [tokens, heads*vdim].
+void attention_window(float* out, const float* Q, const void* kc, const void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0,
+                      const WindowAttn& a, cudaStream_t s);
+// Whole-projection RMS norm of the query rows (in place) and key rows (gains may be null: no norm), key/value rows -> cache rows base + t.
+void qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
+                      DType cache_dt, int tokens, const int* pos_dev, int p0, int qdim, int kdim, int vdim, cudaStream_t s);
+
 // Programmatic dependent launch (PDL): when enabled, kernels are launched with
 // cudaLaunchAttributeProgrammaticStreamSerialization so that a kernel's prologue (barrier init, TMA weight
 // prefetch) overlaps the tail of its predecessor; every kernel executes griddepcontrol.wait before it touches

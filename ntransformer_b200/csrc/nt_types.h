@@ -15,14 +15,16 @@
 namespace nt {
 
 enum class DType : uint8_t {
-    F32 = 0, F16 = 1, Q8_0 = 2, Q4_0 = 3, Q4_K_M = 4, Q6_K = 5, Q5_K = 6, Q2_K = 7, I32 = 8, COUNT
+    F32 = 0, F16 = 1, Q8_0 = 2, Q4_0 = 3, Q4_K_M = 4, Q6_K = 5, Q5_K = 6, Q2_K = 7, I32 = 8,
+    BF16 = 9,      // not a GGUF-reference id: dense bfloat16 rows of safetensors checkpoints (appended, the reference's values are unchanged)
+    COUNT
 };
 
 // Bytes per element (plain types) or per quantisation block (quantised types).
 constexpr size_t dtype_size(DType dt) {
     switch (dt) {
         case DType::F32: case DType::I32: return 4;
-        case DType::F16:    return 2;
+        case DType::F16: case DType::BF16: return 2;
         case DType::Q8_0:   return 34;
         case DType::Q4_0:   return 18;
         case DType::Q4_K_M: return 144;
@@ -48,7 +50,8 @@ inline const char* dtype_name(DType dt) {
         case DType::Q8_0: return "Q8_0";   case DType::Q4_0: return "Q4_0";
         case DType::Q4_K_M: return "Q4_K_M"; case DType::Q5_K: return "Q5_K";
         case DType::Q6_K: return "Q6_K";   case DType::Q2_K: return "Q2_K";
-        case DType::I32: return "I32";     default: return "UNKNOWN";
+        case DType::I32: return "I32";     case DType::BF16: return "BF16";
+        default: return "UNKNOWN";
     }
 }
 

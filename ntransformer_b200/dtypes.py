@@ -12,9 +12,10 @@ class DType(IntEnum):
     Q5_K = 6
     Q2_K = 7
     I32 = 8
+    BF16 = 9      # dense bfloat16 rows (safetensors model folders); appended after the reference's ids
 
 
-_SIZE = {DType.F32: 4, DType.F16: 2, DType.I32: 4, DType.Q8_0: 34, DType.Q4_0: 18, DType.Q4_K_M: 144,
+_SIZE = {DType.F32: 4, DType.F16: 2, DType.BF16: 2, DType.I32: 4, DType.Q8_0: 34, DType.Q4_0: 18, DType.Q4_K_M: 144,
          DType.Q5_K: 176, DType.Q6_K: 210, DType.Q2_K: 84}
 _BLOCK = {DType.Q8_0: 32, DType.Q4_0: 32, DType.Q4_K_M: 256, DType.Q5_K: 256, DType.Q6_K: 256, DType.Q2_K: 256}
 

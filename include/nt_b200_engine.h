@@ -35,6 +35,8 @@ int  nt_model_get_config(nt_model_t m, nt_model_config* out);
 
 /* Model folders (config.json + model.safetensors) of a registered layer-spec family; exact_f32: everything in true 32-bit. */
 nt_model_t nt_model_load_dir(const char* dir, int max_context, int exact_f32);
+/* Host only: validates <dir>/config.json and model.safetensors against each other; text summary (or the reason, with -1) in out. */
+int  nt_model_dir_describe(const char* dir, char* out, size_t cap);
 /* The same family from a config.json TEXT and caller-owned device tensors: create_json -> set_tensor (checkpoint names; matrices
  * F32 / F16 / BF16 row-major, gain vectors F32) -> finalize. */
 nt_model_t nt_model_create_json(const char* config_json, int max_context, int exact_f32);

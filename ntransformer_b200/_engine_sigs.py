@@ -53,6 +53,7 @@ ENGINE_SIGNATURES = {
     "nt_detokenize": (_i, [C.c_char_p, _vp, _i, _vp, _sz]),
     "nt_sample_token": (_i, [_vp, _i, _f, _i, _f, _f, _i, _vp, _i, C.c_uint64]),
     "nt_model_load_dir": (_vp, [C.c_char_p, _i, _i]),
+    "nt_model_dir_describe": (_i, [C.c_char_p, _vp, _sz]),
     "nt_model_create_json": (_vp, [C.c_char_p, _i, _i]),
     "nt_model_forward_logits": (_i, [_vp, _vp, _i, _i, _vp, _i, _vp]),
     "nt_engine_load_path": (_i, [_vp, C.c_char_p, _i, _i]),

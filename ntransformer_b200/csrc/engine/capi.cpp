@@ -5,6 +5,7 @@
 #include "tp_comm.h"
 #include "json.h"
 #include "model_registry.h"
+#include "safetensors.h"
 #include <cstring>
 #include <algorithm>
 #include <memory>
@@ -78,6 +79,35 @@ nt_model_t nt_model_create_json(const char* config_json, int max_context, int ex
     h->model.set_exact_f32(exact_f32 != 0);
     h->model.init(cfg, 0, 1);
     return h;
+}
+// Host only (no GPU touched): reads <dir>/config.json through the family registry and checks model.safetensors against the
+// tensors the configuration needs.  Writes a text summary; returns 0, or -1 with the reason in out.
+int nt_model_dir_describe(const char* dir, char* out, size_t cap) {
+    if (!dir || !out || cap == 0) return -1;
+    auto put = [&](const std::string& t, int rc) { snprintf(out, cap, "%s", t.c_str()); return rc; };
+    ModelConfig cfg;
+    const ModelFamily* fam = nullptr;
+    if (!read_model_dir(dir, cfg, &fam)) return put("config.json rejected", -1);
+    SafeTensorsFile f;
+    if (!f.open(std::string(dir) + "/model.safetensors")) return put("model.safetensors rejected", -1);
+    std::string text = std::string("architecture=") + fam->architecture + " vocab=" + std::to_string(cfg.vocab_size) + " width=" + std::to_string(cfg.hidden_size) +
+                       " layers=" + std::to_string(cfg.n_layers) + " eps=" + std::to_string(cfg.norm_eps) + " mult=" + std::to_string(cfg.residual_mult) + "\n";
+    for (size_t i = 0; i < cfg.layers.size(); i++) {
+        const LayerSpec& L = cfg.layers[i];
+        text += "layer " + std::to_string(i) + ": heads=" + std::to_string(L.heads) + " kv=" + std::to_string(L.kv_heads) + " dim=" + std::to_string(L.dim) +
+                " vdim=" + std::to_string(L.vdim) + " window=" + std::to_string(L.window) + " keep=" + std::to_string(L.keep_first) + " ff=" + std::to_string(L.ff) +
+                " weights_of=" + std::to_string(L.weights_of) + "\n";
+    }
+    size_t n = 0;
+    for (const TensorBinding& b : fam->tensors(cfg)) {
+        const SafeTensorInfo* ti = f.find(b.name);
+        if (!ti) return put("tensor not found: " + b.name, -1);
+        const bool ok = (b.rows == 1 && ti->shape.size() == 1) ? ti->shape[0] == b.cols : (ti->shape.size() == 2 && ti->shape[0] == b.rows && ti->shape[1] == b.cols);
+        if (!ok) return put("tensor " + b.name + " does not have the shape the configuration needs", -1);
+        n++;
+    }
+    text += "tensors=" + std::to_string(n) + "\n";
+    return put(text, 0);
 }
 int nt_model_forward_logits(nt_model_t m, const int* tokens, int n, int start_pos, const int* want, int n_want, float* logits_host) {
     if (!m || !tokens || n < 1 || n_want < 0 || (n_want > 0 && (!want || !logits_host))) return -1;

@@ -52,6 +52,57 @@ class Model:
             raise RuntimeError("model is missing tensors")
         return cls(h, cfg, keep=tensors, tp_rank=tp_rank, tp_size=tp_size)
 
+    # ---- layer-spec families: a model folder (config.json + model.safetensors) or a config dict + device tensors ----
+    @classmethod
+    def _wrap_spec(cls, h, keep=None) -> "Model":
+        c = ModelConfigC()
+        lib().nt_model_get_config(h, C.byref(c))
+        cfg = LlamaConfig(**{n: getattr(c, n) for n, _ in ModelConfigC._fields_})
+        return cls(h, cfg, keep=keep)
+
+    @classmethod
+    def load_dir(cls, path: str, max_context: int = 4096, exact_f32: bool = False) -> "Model":
+        h = lib().nt_model_load_dir(str(path).encode(), max_context, int(exact_f32))
+        if not h:
+            raise RuntimeError(f"failed to load {path}")
+        return cls._wrap_spec(h)
+
+    @classmethod
+    def from_config_json(cls, config: dict, tensors: dict, max_context: int = 4096, exact_f32: bool = False) -> "Model":
+        """config: the family's config.json as a dict; tensors: checkpoint name -> torch CUDA tensor (matrices float32 / float16 /
+        bfloat16 [out, in], gain vectors float32)."""
+        import json
+
+        import torch
+
+        h = lib().nt_model_create_json(json.dumps(config).encode(), max_context, int(exact_f32))
+        if not h:
+            raise ValueError("engine rejected the configuration")
+        ids = {torch.float32: DType.F32, torch.float16: DType.F16, torch.bfloat16: DType.BF16}
+        keep = {}
+        for name, t in tensors.items():
+            t = t.contiguous()
+            keep[name] = t
+            if lib().nt_model_set_tensor(h, name.encode(), t.data_ptr(), int(ids[t.dtype]), 0) != 0:
+                lib().nt_model_free(h)
+                raise ValueError(f"engine rejected tensor {name}")
+        torch.cuda.synchronize()
+        if lib().nt_model_finalize(h) != 0:
+            lib().nt_model_free(h)
+            raise RuntimeError("model is missing tensors")
+        return cls._wrap_spec(h, keep=keep)
+
+    def forward_logits(self, tokens, start_pos: int, want):
+        """Runs the tokens at positions start_pos.. and returns HOST logits [len(want), vocab] at the wanted places (ascending
+        indices into tokens)."""
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        w = np.ascontiguousarray(want, dtype=np.int32)
+        out = np.empty((len(w), self.cfg.vocab_size), dtype=np.float32)
+        rc = lib().nt_model_forward_logits(self._h, toks.ctypes.data_as(C.c_void_p), len(toks), start_pos, w.ctypes.data_as(C.c_void_p), len(w),
+                                           out.ctypes.data_as(C.c_void_p))
+        assert rc == 0
+        return out
+
     @classmethod
     def synthetic(cls, cfg: LlamaConfig, mix: str, seed: int = 1234, tp_rank: int = 0, tp_size: int = 1, device="cuda") -> "Model":
         """Random valid GGUF blocks generated directly on the GPU (no checkpoint or file involved)."""
@@ -212,6 +263,20 @@ class Engine:
 
     def load(self, path: str) -> bool:
         return lib().nt_engine_load(self._h, str(path).encode()) == 0
+
+    def load_path(self, path: str, max_context: int = 4096, exact_f32: bool = False) -> bool:
+        """A GGUF file or a model folder (config.json + model.safetensors)."""
+        return lib().nt_engine_load_path(self._h, str(path).encode(), max_context, int(exact_f32)) == 0
+
+    def generate_ids(self, prompt_ids, max_tokens=32, temperature=0.0, top_k=40, top_p=0.9, repeat_penalty=1.0, seed=42):
+        """The generation loop over token ids (prompt pass, then step by step with the engine's sampler); returns the new ids."""
+        ids = np.ascontiguousarray(prompt_ids, dtype=np.int32)
+        out = np.empty(max(max_tokens, 1), dtype=np.int32)
+        n = lib().nt_engine_generate_ids(self._h, ids.ctypes.data_as(C.c_void_p), len(ids), max_tokens, temperature, top_k, top_p, repeat_penalty,
+                                         seed, out.ctypes.data_as(C.c_void_p), len(out))
+        if n < 0:
+            raise RuntimeError("generate_ids failed")
+        return out[:n].tolist()
 
     def generate(self, prompt: str, max_tokens=32, temperature=0.0, top_k=40, top_p=0.9) -> str:
         p = lib().nt_engine_generate(self._h, prompt.encode(), max_tokens, temperature, top_k, top_p)

@@ -94,9 +94,11 @@ def random_model(rng: np.random.Generator, *, vocab=96, width=64, n_layers=3, he
     """A small random configuration + weights (bf16-representable values). share: {layer: source layer}."""
     import torch
 
+    def bf(a):
+        return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+
     def r(*shape, s=1.0):
-        a = rng.standard_normal(shape).astype(np.float32) * s
-        return torch.from_numpy(a).to(torch.bfloat16).to(torch.float32).numpy()
+        return bf(rng.standard_normal(shape).astype(np.float32) * s)
 
     share = share or {}
     layers, W = [], {}
@@ -111,21 +113,21 @@ def random_model(rng: np.random.Generator, *, vocab=96, width=64, n_layers=3, he
             continue
         layers.append(entry)
         p = "l%d." % i
-        W[p + "norm1"] = 1.0 + r(width, s=0.1)
+        W[p + "norm1"] = bf(1.0 + r(width, s=0.1))
         W[p + "mix.q"] = r(heads * dim, width, s=width ** -0.5)
         W[p + "mix.k"] = r(kv_heads * dim, width, s=width ** -0.5)
         W[p + "mix.v"] = r(kv_heads * vdim, width, s=width ** -0.5)
-        W[p + "mix.q.norm"] = 1.0 + r(heads * dim, s=0.1)
-        W[p + "mix.k.norm"] = 1.0 + r(kv_heads * dim, s=0.1)
+        W[p + "mix.q.norm"] = bf(1.0 + r(heads * dim, s=0.1))
+        W[p + "mix.k.norm"] = bf(1.0 + r(kv_heads * dim, s=0.1))
         W[p + "mix.o"] = r(width, heads * vdim, s=(heads * vdim) ** -0.5)
-        W[p + "ls1"] = 1.0 + r(width, s=0.2)
+        W[p + "ls1"] = bf(1.0 + r(width, s=0.2))
         if i not in no_mlp:
             W[p + "mlp.gate"] = r(ff, width, s=width ** -0.5)
             W[p + "mlp.up"] = r(ff, width, s=width ** -0.5)
             W[p + "mlp.down"] = r(width, ff, s=ff ** -0.5)
-            W[p + "ls2"] = 1.0 + r(width, s=0.2)
+            W[p + "ls2"] = bf(1.0 + r(width, s=0.2))
     W["embed"] = r(vocab, width)
-    W["final.norm"] = 1.0 + r(width, s=0.1)
+    W["final.norm"] = bf(1.0 + r(width, s=0.1))
     W["head"] = r(vocab, width, s=width ** -0.5)
     cfg = {"architecture": "Zelunex", "layers": layers, "norm": {"eps": eps}, "residual_mult": mult, "vocab": vocab, "width": width}
     return cfg, W

@@ -749,6 +749,71 @@ def run_check(args, rank, world):
         sys.exit(1)
 
 
+FAMILY_SIZES = {
+    # name: (width, heads, kv_heads, head dim, ff); 4 layers of each, vocabulary 32000, random weights
+    "2048x8192": (2048, 16, 4, 128, 8192),
+    "4096x14336": (4096, 32, 8, 128, 14336),
+}
+
+
+def run_family_compare(args):
+    """--family-compare: prompt-pass and decode throughput of the Zelunex family (BF16 weights, windowed attention) beside the
+    closest GGUF family member (Llama block, F16 weights, full causal attention) at equal layer sizes.  Device-timed with CUDA
+    events on the model's stream; prompts differ between steps and the weights of either model exceed L2."""
+    import torch
+    from dataclasses import replace
+    from ntransformer_b200 import kernels as K
+    from ntransformer_b200.engine import Model
+    from ntransformer_b200.model_spec import LLAMA3_8B, zelunex_config, zelunex_random_tensors
+
+    torch.cuda.set_device(0)
+    n_layers, vocab, prompt_len, max_seq, window = 4, 32000, 2048, 4096, 1024
+    hbm, hbm_src = measured_peak_hbm()
+    rows = []
+    for name, (width, heads, kv, dim, ff) in FAMILY_SIZES.items():
+        zc = zelunex_config(vocab=vocab, width=width, n_layers=n_layers, heads=heads, kv_heads=kv, dim=dim, vdim=dim, ff=ff, window=window)
+        lc = replace(LLAMA3_8B, vocab_size=vocab, hidden_size=width, intermediate_size=ff, n_layers=n_layers, n_heads=heads, n_kv_heads=kv, head_dim=dim,
+                     max_seq_len=max_seq)
+        row = {"size": name, "layers": n_layers, "prompt_tokens": prompt_len, "decode_context": prompt_len, "window": window}
+        for label, make in (("zelunex_bf16", lambda: Model.from_config_json(zc, zelunex_random_tensors(zc), max_context=max_seq)),
+                            ("llama_f16", lambda: Model.synthetic(lc, "F16", seed=1234))):
+            model = make()
+            stream = torch.cuda.ExternalStream(model.stream)
+            prompts = [[token_at(i + 97 * j, vocab) for i in range(prompt_len)] for j in range(4)]
+            for i in range(args.warmup):
+                model.forward_async(prompts[i % 4], 0)
+            model.sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n0 = K.launch_count()
+            psteps = max(3, min(args.steps, 8))
+            a.record(stream)
+            for i in range(psteps):
+                model.forward_async(prompts[i % 4], 0)
+            b.record(stream)
+            model.sync()
+            prefill = psteps * prompt_len / (a.elapsed_time(b) / 1e3)
+            dsteps = max(8, min(args.steps, 256))
+            for i in range(args.warmup):
+                model.forward_async([token_at(i, vocab)], prompt_len + i)
+            model.sync()
+            a.record(stream)
+            for i in range(dsteps):
+                model.forward_async([token_at(i + 5, vocab)], prompt_len + args.warmup + i)
+            b.record(stream)
+            model.sync()
+            ms = a.elapsed_time(b) / dsteps
+            bpt = model.bytes_per_token(prompt_len + args.warmup + dsteps // 2)
+            row[label] = {"prefill_tok_s": round(prefill, 1), "decode_tok_s": round(1e3 / ms, 1), "decode_ms": round(ms, 4),
+                          "decode_bytes_per_token": bpt, "decode_frac_of_hbm_peak": round(bpt / (ms * 1e-3) / (hbm * 1e9), 3),
+                          "launches": int(K.launch_count() - n0)}
+            model.close()
+            del model
+            torch.cuda.empty_cache()
+        rows.append(row)
+    print(json.dumps({"metric": "family_compare", "unit": "tok/s", "hbm_peak_gbs": hbm, "hbm_peak_source": hbm_src, "dtype": "bf16 / f16 weights, f32 activations",
+                      "data": "synthetic", "rows": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -765,6 +830,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="--check only: keep this many layers of the workload's shape (0 = all)")
     ap.add_argument("--oracle-steps", type=int, default=0, help="--check only: also run the F64-accumulating CPU oracle for the prompt and this many steps")
     ap.add_argument("--all-errs", action="store_true", help="--check only: list the error of every step, not the first 8")
+    ap.add_argument("--family-compare", action="store_true",
+                    help="instead of the workload: Zelunex beside the Llama block at equal layer sizes, prompt pass and decode (1 GPU)")
     ap.add_argument("--per-token-prompt", action="store_true", help="--check only: our engine replays the prompt token by token like the reference")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -772,7 +839,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     if world != args.gpus and world == 1 and args.gpus > 1:
         sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
-    if args.check:
+    if args.family_compare:
+        if rank == 0:
+            run_family_compare(args)
+    elif args.check:
         run_check(args, rank, world)
     elif args.impl == "reference":
         run_reference(args, rank, world)

@@ -238,12 +238,36 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     pf_.g = dmalloc<float>(T * ffmax); pf_.u = dmalloc<float>(T * ffmax);
     pf_.tok = dmalloc<int>(T);
     pf_.ws = pf_.ws2 = pf_.hws = nullptr;
+    bool any_tc = false;
+    for (int i = 0; i < cfg_.n_layers; i++) {
+        const LayerWeights& L = layer_weights(i);
+        for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down}) any_tc = any_tc || (w->ptr && spec_tc_ok(*w));
+    }
+    if (any_tc) {                         // BF16 hi/lo splits of the three GEMM inputs (normed block input, attention output, gated activation)
+        pf_.hws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)hidden));
+        pf_.ws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)omax));
+        pf_.ws2 = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)ffmax));
+    }
     pf_.cap = (int)T;
 }
 
-bool Model::spec_tc_ok(const Weight&) const { return false; }
+// BF16 rows that the tcgen05 GEMM can read in place through TMA (rows % 128, cols % 64, 16-byte aligned); never in exact mode.
+bool Model::spec_tc_ok(const Weight& w) const {
+    static const bool off = getenv("NT_B200_NO_TC_PREFILL") != nullptr;
+    return !exact32_ && !off && w.dtype == DType::BF16 && gemm_f16_tc_supported(w.ptr, w.rows, w.cols, w.pitch);
+}
 
-void Model::spec_gemm(float* C, const float* A, const void*, const Weight& w, int T, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s) {
+// C (ep)= A . W^T for T prompt rows: on the tensor cores from the BF16 hi/lo split of A when the matrix qualifies, else in FP32
+// on CUDA cores from A itself.  Either input may be null when the caller knows which path the matrix takes.
+void Model::spec_gemm(float* C, const float* A, const void* A_split, const Weight& w, int T, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s) {
+    if (A_split && spec_tc_ok(w)) {
+        TcOpts o;
+        o.bf16 = true;
+        if (ep == DENSE_SCALED_ADD) { o.col_scale = row_scale; o.alpha = alpha; }
+        NT_CHECK(gemm_f16_tc_ws(C, A_split, w.ptr, T, w.rows, w.cols, ep != DENSE_STORE, s, o), "prefill GEMM rejected");
+        return;
+    }
+    NT_CHECK(A != nullptr, "spec_gemm: the FP32 input of a CUDA-core GEMM is missing");
     gemm_dense(C, A, w.ptr, w.dtype, w.pitch, T, w.rows, w.cols, ep, row_scale, alpha, s);
 }
 
@@ -264,19 +288,37 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
         for (int i = 0; i < cfg_.n_layers; i++) {
             const LayerSpec& S = cfg_.layers[(size_t)i];
             const LayerWeights& L = layer_weights(i);
-            rmsnorm(pf_.h, pf_.x, L.attn_norm, T, hidden, cfg_.norm_eps, s);
-            spec_gemm(pf_.q, pf_.h, pf_.hws, L.wq, T, DENSE_STORE, nullptr, 1.f, s);
-            spec_gemm(pf_.k, pf_.h, pf_.hws, L.wk, T, DENSE_STORE, nullptr, 1.f, s);
-            spec_gemm(pf_.v, pf_.h, pf_.hws, L.wv, T, DENSE_STORE, nullptr, 1.f, s);
+            // the block's normed input feeds q, k, v, gate and up: as FP32 rows, as a BF16 split, or both, by what those matrices take
+            bool h_f32 = false, h_split = false;
+            for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.gate, &L.up})
+                if (w->ptr && (w == &L.wq || w == &L.wk || w == &L.wv || S.ff > 0)) (spec_tc_ok(*w) ? h_split : h_f32) = true;
+            if (h_f32) rmsnorm(pf_.h, pf_.x, L.attn_norm, T, hidden, cfg_.norm_eps, s);
+            if (h_split) rmsnorm_split(pf_.hws, pf_.x, L.attn_norm, T, hidden, cfg_.norm_eps, s, true);
+            const float* hf = h_f32 ? pf_.h : nullptr;
+            const void* hs = h_split ? pf_.hws : nullptr;
+            spec_gemm(pf_.q, hf, hs, L.wq, T, DENSE_STORE, nullptr, 1.f, s);
+            spec_gemm(pf_.k, hf, hs, L.wk, T, DENSE_STORE, nullptr, 1.f, s);
+            spec_gemm(pf_.v, hf, hs, L.wv, T, DENSE_STORE, nullptr, 1.f, s);
             qk_norm_kv_write(pf_.q, pf_.k, pf_.v, L.q_norm, L.k_norm, cfg_.norm_eps, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, T, nullptr, p0,
                              S.heads * S.dim, S.kv_heads * S.dim, S.kv_heads * S.vdim, s);
             attention_window(pf_.attn, pf_.q, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, T, nullptr, p0, attn_of(S), s);
-            spec_gemm(pf_.x, pf_.attn, nullptr, L.wo, T, DENSE_SCALED_ADD, L.ls1, m, s);
+            const bool o_tc = spec_tc_ok(L.wo);
+            if (o_tc) split_activations(pf_.ws, pf_.attn, T, S.heads * S.vdim, s, true);
+            spec_gemm(pf_.x, pf_.attn, o_tc ? pf_.ws : nullptr, L.wo, T, DENSE_SCALED_ADD, L.ls1, m, s);
             if (S.ff > 0) {
-                spec_gemm(pf_.g, pf_.h, pf_.hws, L.gate, T, DENSE_STORE, nullptr, 1.f, s);
-                spec_gemm(pf_.u, pf_.h, pf_.hws, L.up, T, DENSE_STORE, nullptr, 1.f, s);
-                glu_mul(pf_.g, pf_.g, pf_.u, (size_t)T * S.ff, S.act == GluAct::GELU_TANH, s);
-                spec_gemm(pf_.x, pf_.g, nullptr, L.down, T, DENSE_SCALED_ADD, L.ls2, m, s);
+                const bool gelu = S.act == GluAct::GELU_TANH, down_tc = spec_tc_ok(L.down);
+                if (spec_tc_ok(L.gate) && spec_tc_ok(L.up) && down_tc) {
+                    // gate / up GEMMs with the gated activation and the split for the down projection in the epilogue: the
+                    // [T, ff] activations never reach HBM in FP32
+                    TcOpts o; o.bf16 = true; o.gelu = gelu;
+                    NT_CHECK(gemm_f16_tc_swiglu_ws(pf_.ws2, pf_.hws, L.gate.ptr, L.up.ptr, T, S.ff, hidden, s, o), "prefill GEMM (gate/up) rejected");
+                } else {
+                    spec_gemm(pf_.g, hf, hs, L.gate, T, DENSE_STORE, nullptr, 1.f, s);
+                    spec_gemm(pf_.u, hf, hs, L.up, T, DENSE_STORE, nullptr, 1.f, s);
+                    glu_mul(pf_.g, pf_.g, pf_.u, (size_t)T * S.ff, gelu, s);
+                    if (down_tc) split_activations(pf_.ws2, pf_.g, T, S.ff, s, true);
+                }
+                spec_gemm(pf_.x, pf_.g, down_tc ? pf_.ws2 : nullptr, L.down, T, DENSE_SCALED_ADD, L.ls2, m, s);
             }
         }
         if (!want_.empty()) emit_wanted(pf_.x, c0, T, s);

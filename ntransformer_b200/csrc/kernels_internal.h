@@ -173,12 +173,16 @@ inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
 size_t gemm_f16_tc_workspace_bytes(int M, int K);
 bool gemm_f16_tc(float* C, const float* A, const void* W_f16, int M, int N, int K, void* workspace, cudaStream_t s);
 bool gemm_f16_tc_supported(const void* W_f16, int N, int K, size_t row_pitch);
-void split_activations(void* workspace, const float* A, int M, int K, cudaStream_t s);
-bool gemm_f16_tc_ws(float* C, const void* workspace, const void* W_f16, int M, int N, int K, bool add, cudaStream_t s);
+// Variants of the tensor-core GEMM: bf16 — weights and the activation split are BF16 (safetensors families; the same 16-bit
+// layouts, only the MMA's operand format changes); gelu — the gated epilogue uses tanh-GELU instead of SiLU; col_scale / alpha —
+// the store / add epilogue writes C (+)= alpha * col_scale[n] * (A.W^T) (per-channel layer scale and residual multiplier).
+struct TcOpts { bool bf16 = false; bool gelu = false; const float* col_scale = nullptr; float alpha = 1.0f; };
+void split_activations(void* workspace, const float* A, int M, int K, cudaStream_t s, bool bf16 = false);
+bool gemm_f16_tc_ws(float* C, const void* workspace, const void* W_f16, int M, int N, int K, bool add, cudaStream_t s, const TcOpts& o = TcOpts());
 // workspace_out <- split(silu(A.Wgate^T) * (A.Wup^T)): the FFN's gate/up GEMMs with the SwiGLU + split fused in the epilogue
 bool gemm_f16_tc_swiglu_ws(void* workspace_out, const void* workspace_in, const void* Wgate_f16, const void* Wup_f16, int M, int N, int K,
-                           cudaStream_t s);
-void rmsnorm_split(void* workspace, const float* x, const float* w, int rows, int hidden, float eps, cudaStream_t s);
+                           cudaStream_t s, const TcOpts& o = TcOpts());
+void rmsnorm_split(void* workspace, const float* x, const float* w, int rows, int hidden, float eps, cudaStream_t s, bool bf16 = false);
 // prefill_dequant.cu: any GGUF weight matrix -> dense F16 pair with W = w_hi + w_lo (operands of two tensor-core GEMMs)
 bool dequant_split_supported(DType dt);
 void dequant_split(void* w_hi, void* w_lo, const void* W, DType dt, size_t row_pitch, int rows, int cols, cudaStream_t s);

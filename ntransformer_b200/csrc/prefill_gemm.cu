@@ -14,6 +14,7 @@
 #include "ring.cuh"
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <cuda_bf16.h>
 #include <mutex>
 
 namespace nt { namespace b200 {
@@ -36,10 +37,36 @@ template <int BN> struct Cfg {
     static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
 
+// the gated unit's activation: SiLU, or tanh-GELU written through exp (tanh u = 1 - 2 / (e^{2u} + 1); saturates cleanly at both ends)
+__device__ __forceinline__ float gate_act(float g, int gelu) {
+    if (!gelu) return g / (1.0f + expf(-g));
+    const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (2.0f - 2.0f / (expf(2.0f * u) + 1.0f));
+}
 // a = hi + lo with hi = f16(a), lo = f16(a - hi): 4 floats per thread
-__global__ void split_f32_kernel(__half2* __restrict__ hi, __half2* __restrict__ lo, const float4* __restrict__ a, size_t n4) {
+// The same split into two BF16 values (operands of the BF16 tensor-core form, ~16 mantissa bits together): packed pair of 16-bit words
+__device__ __forceinline__ void split_pair(float a, float b, int bf16, uint32_t& hi, uint32_t& lo) {
+    if (bf16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        const float2 f = __bfloat1622float2(h);
+        const __nv_bfloat162 l = __floats2bfloat162_rn(a - f.x, b - f.y);
+        hi = *reinterpret_cast<const uint32_t*>(&h); lo = *reinterpret_cast<const uint32_t*>(&l);
+    } else {
+        const __half2 h = __floats2half2_rn(a, b);
+        const float2 f = __half22float2(h);
+        const __half2 l = __floats2half2_rn(a - f.x, b - f.y);
+        hi = *reinterpret_cast<const uint32_t*>(&h); lo = *reinterpret_cast<const uint32_t*>(&l);
+    }
+}
+__global__ void split_f32_kernel(__half2* __restrict__ hi, __half2* __restrict__ lo, const float4* __restrict__ a, size_t n4, int bf16) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n4) {
+    if (i < n4 && bf16) {
+        const float4 v = a[i];
+        uint32_t h0, l0, h1, l1;
+        split_pair(v.x, v.y, 1, h0, l0); split_pair(v.z, v.w, 1, h1, l1);
+        reinterpret_cast<uint2*>(hi)[i] = make_uint2(h0, h1);
+        reinterpret_cast<uint2*>(lo)[i] = make_uint2(l0, l1);
+    } else if (i < n4) {
         const float4 v = a[i];
         const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
         const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
@@ -118,10 +145,11 @@ __global__ void __launch_bounds__(192, 1) gemm_f16_tc_kernel(const __grid_consta
                                                              const __grid_constant__ CUtensorMap map_b2,
                                                              float* __restrict__ C, __half* __restrict__ split_out,
                                                              int M, int Mp, int N, int K, int tiles_m, int tiles_n, int n_tiles, int n_outer,
-                                                             int kc_blocks) {
+                                                             int kc_blocks, int bf16, int gelu, const float* __restrict__ col_scale, float alpha) {
     constexpr int STAGES = Cfg<BN>::STAGES, STAGE_BYTES = Cfg<BN>::STAGE_BYTES, TMEM_COLS = 2 * BN;
     constexpr int TN = MODE == MODE_SWIGLU ? 128 : BN;          // output columns per tile
-    constexpr uint32_t IDESC = MODE == MODE_SWIGLU ? Cfg<128>::IDESC : Cfg<BN>::IDESC;
+    // BF16 operands: A format at [7,10) and B format at [10,13) become 1 (F16 = 0); layouts, strides and the F32 accumulator are the same
+    const uint32_t IDESC = (MODE == MODE_SWIGLU ? Cfg<128>::IDESC : Cfg<BN>::IDESC) | (bf16 ? ((1u << 7) | (1u << 10)) : 0u);
     static_assert(MODE != MODE_SWIGLU || BN == 256, "SwiGLU tiles pair 128 gate with 128 up columns");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -224,13 +252,9 @@ __global__ void __launch_bounds__(192, 1) gemm_f16_tc_kernel(const __grid_consta
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
                                 const float g0 = __uint_as_float(v[j + 2 * e]), g1 = __uint_as_float(v[j + 2 * e + 1]);
-                                const float a0 = g0 / (1.0f + expf(-g0)) * __uint_as_float(u[j + 2 * e]);      // elementwise.cu silu_mul
-                                const float a1 = g1 / (1.0f + expf(-g1)) * __uint_as_float(u[j + 2 * e + 1]);
-                                const __half2 h = __floats2half2_rn(a0, a1);
-                                const float2 f = __half22float2(h);
-                                const __half2 l = __floats2half2_rn(a0 - f.x, a1 - f.y);
-                                ph[e] = *reinterpret_cast<const uint32_t*>(&h);
-                                pl[e] = *reinterpret_cast<const uint32_t*>(&l);
+                                const float a0 = gate_act(g0, gelu) * __uint_as_float(u[j + 2 * e]);      // elementwise.cu silu_mul / tanh-GELU gate
+                                const float a1 = gate_act(g1, gelu) * __uint_as_float(u[j + 2 * e + 1]);
+                                split_pair(a0, a1, bf16, ph[e], pl[e]);
                             }
                             *reinterpret_cast<uint4*>(hi + j) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
                             *reinterpret_cast<uint4*>(lo + j) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
@@ -244,6 +268,10 @@ __global__ void __launch_bounds__(192, 1) gemm_f16_tc_kernel(const __grid_consta
                         for (int j = 0; j < 32; j += 4) {
                             float4* dst = reinterpret_cast<float4*>(crow + j);
                             float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                            if (col_scale || alpha != 1.0f) {           // C (+)= alpha * col_scale[n] * acc: layer scale and residual multiplier
+                                const float4 g = col_scale ? *reinterpret_cast<const float4*>(col_scale + n0 + c * 32 + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+                                o.x *= alpha * g.x; o.y *= alpha * g.y; o.z *= alpha * g.z; o.w *= alpha * g.w;
+                            }
                             if (add_c) { const float4 r = *dst; o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w; }   // residual / earlier chunks
                             *dst = o;
                         }
@@ -263,7 +291,7 @@ __global__ void __launch_bounds__(192, 1) gemm_f16_tc_kernel(const __grid_consta
 
 // RMSNorm (rmsnorm.cu:17-70 math) writing the F16 hi/lo split the GEMM consumes: one CTA per row
 __global__ void __launch_bounds__(512) rmsnorm_split_kernel(__half* __restrict__ hi, __half* __restrict__ lo, const float* __restrict__ xin,
-                                                            const float* __restrict__ w, int hidden, float eps) {
+                                                            const float* __restrict__ w, int hidden, float eps, int bf16) {
     __shared__ float red[16];
     const float* x = xin + (size_t)blockIdx.x * hidden;
     float ss = 0.f;
@@ -279,10 +307,10 @@ __global__ void __launch_bounds__(512) rmsnorm_split_kernel(__half* __restrict__
     for (int i = threadIdx.x; i < hidden / 2; i += blockDim.x) {
         const float2 xv = reinterpret_cast<const float2*>(x)[i], wv = reinterpret_cast<const float2*>(w)[i];
         const float a = xv.x * rms_inv * wv.x, b = xv.y * rms_inv * wv.y;
-        const __half2 h = __floats2half2_rn(a, b);
-        const float2 f = __half22float2(h);
-        h2[i] = h;
-        l2[i] = __floats2half2_rn(a - f.x, b - f.y);
+        uint32_t ph, pl;
+        split_pair(a, b, bf16, ph, pl);
+        reinterpret_cast<uint32_t*>(h2)[i] = ph;
+        reinterpret_cast<uint32_t*>(l2)[i] = pl;
     }
 }
 
@@ -301,14 +329,14 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 // 2-D F16 tensor [rows][cols] (cols contiguous), box = 64 cols x box_rows rows (<= 256), 128-byte swizzle
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool bf16 = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
     const cuuint32_t box[2] = {BK, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -325,22 +353,22 @@ bool gemm_f16_tc_supported(const void* W_f16, int N, int K, size_t row_pitch) {
 }
 
 // workspace <- F16 hi/lo split of A[M,K] (rows padded with zeros to a multiple of 128)
-void split_activations(void* workspace, const float* A, int M, int K, cudaStream_t s) {
+void split_activations(void* workspace, const float* A, int M, int K, cudaStream_t s, bool bf16) {
     const size_t Mp = ((size_t)M + BM - 1) / BM * BM;
     __half* hi = static_cast<__half*>(workspace);
     __half* lo = hi + Mp * (size_t)K;
     if (Mp != (size_t)M) NT_CUDA_CHECK(cudaMemsetAsync(workspace, 0, gemm_f16_tc_workspace_bytes(M, K), s));
     const size_t n4 = (size_t)M * K / 4;
     split_f32_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, s>>>(reinterpret_cast<__half2*>(hi), reinterpret_cast<__half2*>(lo),
-                                                                  reinterpret_cast<const float4*>(A), n4);
+                                                                  reinterpret_cast<const float4*>(A), n4, bf16 ? 1 : 0);
     count_launch();
 }
 
 // rmsnorm(x) * w for `rows` rows, written straight into the split workspace
-void rmsnorm_split(void* workspace, const float* x, const float* w, int rows, int hidden, float eps, cudaStream_t s) {
+void rmsnorm_split(void* workspace, const float* x, const float* w, int rows, int hidden, float eps, cudaStream_t s, bool bf16) {
     const size_t Mp = ((size_t)rows + BM - 1) / BM * BM;
     __half* hi = static_cast<__half*>(workspace);
-    rmsnorm_split_kernel<<<rows, 512, 0, s>>>(hi, hi + Mp * (size_t)hidden, x, w, hidden, eps);
+    rmsnorm_split_kernel<<<rows, 512, 0, s>>>(hi, hi + Mp * (size_t)hidden, x, w, hidden, eps, bf16 ? 1 : 0);
     count_launch();
 }
 
@@ -354,11 +382,11 @@ int sm_count() {
 
 template <int BN, int MODE>
 bool launch_gemm(float* C, __half* split_out, const void* workspace, const void* W, const void* W2, int M, size_t Mp, int N, int K,
-                 cudaStream_t s) {
+                 cudaStream_t s, const TcOpts& o = TcOpts()) {
     constexpr int TN = MODE == MODE_SWIGLU ? 128 : BN;
     CUtensorMap map_a, map_b, map_b2;
-    if (!make_map(&map_a, workspace, 2 * Mp, (uint64_t)K, BM) || !make_map(&map_b, W, (uint64_t)N, (uint64_t)K, TN) ||
-        !make_map(&map_b2, W2 ? W2 : W, (uint64_t)N, (uint64_t)K, TN))
+    if (!make_map(&map_a, workspace, 2 * Mp, (uint64_t)K, BM, o.bf16) || !make_map(&map_b, W, (uint64_t)N, (uint64_t)K, TN, o.bf16) ||
+        !make_map(&map_b2, W2 ? W2 : W, (uint64_t)N, (uint64_t)K, TN, o.bf16))
         return false;
     static unsigned long long configured = 0;      // bit per device id
     opt_in_dynamic_smem(gemm_f16_tc_kernel<BN, MODE>, (int)(Cfg<BN>::SMEM), configured);
@@ -377,7 +405,7 @@ bool launch_gemm(float* C, __half* split_out, const void* workspace, const void*
     static const int kc_env = [] { const char* e = getenv("NT_B200_GEMM_KC"); return e ? atoi(e) : 64; }();
     const int kc_blocks = kc_env > 0 ? kc_env : K / BK;
     gemm_f16_tc_kernel<BN, MODE><<<grid, 192, Cfg<BN>::SMEM, s>>>(map_a, map_b, map_b2, C, split_out, M, (int)Mp, N, K, tiles_m, tiles_n,
-                                                                 n_tiles, n_outer, kc_blocks);
+                                                                 n_tiles, n_outer, kc_blocks, o.bf16 ? 1 : 0, o.gelu ? 1 : 0, o.col_scale, o.alpha);
     count_launch();
     return true;
 }
@@ -385,23 +413,23 @@ bool launch_gemm(float* C, __half* split_out, const void* workspace, const void*
 }  // namespace
 
 // C[M,N] (+)= split(A)[M,K] . W[N,K]^T with A already split into `workspace`
-bool gemm_f16_tc_ws(float* C, const void* workspace, const void* W_f16, int M, int N, int K, bool add, cudaStream_t s) {
+bool gemm_f16_tc_ws(float* C, const void* workspace, const void* W_f16, int M, int N, int K, bool add, cudaStream_t s, const TcOpts& o) {
     if (M <= 0 || !gemm_f16_tc_supported(W_f16, N, K, 0)) return false;
     const size_t Mp = ((size_t)M + BM - 1) / BM * BM;
     static const bool force128 = getenv("NT_B200_GEMM_BN128") != nullptr;
     if (N % 256 == 0 && !force128)
-        return add ? launch_gemm<256, MODE_ADD>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s)
-                   : launch_gemm<256, MODE_STORE>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s);
-    return add ? launch_gemm<128, MODE_ADD>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s)
-               : launch_gemm<128, MODE_STORE>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s);
+        return add ? launch_gemm<256, MODE_ADD>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s, o)
+                   : launch_gemm<256, MODE_STORE>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s, o);
+    return add ? launch_gemm<128, MODE_ADD>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s, o)
+               : launch_gemm<128, MODE_STORE>(C, nullptr, workspace, W_f16, nullptr, M, Mp, N, K, s, o);
 }
 
 // workspace_out <- split(silu(A.Wgate^T) * (A.Wup^T)) for A already split into workspace_in; N = rows of Wgate/Wup
 bool gemm_f16_tc_swiglu_ws(void* workspace_out, const void* workspace_in, const void* Wgate_f16, const void* Wup_f16, int M, int N, int K,
-                           cudaStream_t s) {
+                           cudaStream_t s, const TcOpts& o) {
     if (M <= 0 || !gemm_f16_tc_supported(Wgate_f16, N, K, 0) || !gemm_f16_tc_supported(Wup_f16, N, K, 0)) return false;
     const size_t Mp = ((size_t)M + BM - 1) / BM * BM;
-    return launch_gemm<256, MODE_SWIGLU>(nullptr, static_cast<__half*>(workspace_out), workspace_in, Wgate_f16, Wup_f16, M, Mp, N, K, s);
+    return launch_gemm<256, MODE_SWIGLU>(nullptr, static_cast<__half*>(workspace_out), workspace_in, Wgate_f16, Wup_f16, M, Mp, N, K, s, o);
 }
 
 // C[M,N] = A[M,K] . W[N,K]^T ; N % 128 == 0, K % 64 == 0; workspace >= gemm_f16_tc_workspace_bytes(M, K)

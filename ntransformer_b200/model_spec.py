@@ -87,3 +87,56 @@ def bytes_per_token(cfg: LlamaConfig, mix: str, ctx: int, tp_size: int = 1) -> i
             continue
         b += r * (c * 4 if dt == DType.F32 and r == 1 else dtype_row_size(dt, c))
     return b + 2 * cfg.n_layers * ctx * (cfg.n_kv_heads // tp_size) * cfg.head_dim * 2
+
+
+# ---- Zelunex (layer-spec family, model folders): synthetic configurations and random device weights for benchmarks ----
+def zelunex_config(vocab=32000, width=4096, n_layers=4, heads=32, kv_heads=8, dim=128, vdim=128, ff=14336, window=1024, keep_first=4,
+                   softcap=30.0, eps=1e-5, residual_mult=0.7, share=None):
+    """The family's config.json as a dict.  share: {layer: earlier layer whose tensors it reads}."""
+    share = share or {}
+    layers = []
+    for i in range(n_layers):
+        e = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "softcap": softcap,
+                       "mask": {"size": window, "keep_first": keep_first}},
+             "mlp": {"kind": "dense", "ff": ff} if ff else None}
+        if i in share:
+            e["weights_of"] = share[i]
+        layers.append(e)
+    return {"architecture": "Zelunex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "residual_mult": residual_mult, "layers": layers}
+
+
+def zelunex_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype=None):
+    """Checkpoint name -> random CUDA tensor (matrices `dtype`, default bfloat16; gain vectors float32)."""
+    import torch
+
+    dtype = dtype or torch.bfloat16
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W = config["width"]
+
+    def mat(rows, cols):
+        return (torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32) * cols ** -0.5).to(dtype)
+
+    def vec(n):
+        return 1.0 + 0.1 * torch.randn(n, generator=g, device=device, dtype=torch.float32)
+
+    t = {"embed": mat(config["vocab"], W) * W ** 0.5, "final.norm": vec(W), "head": mat(config["vocab"], W)}
+    for i, e in enumerate(config["layers"]):
+        if "weights_of" in e:
+            continue
+        m, p = e["mixer"], "l%d." % i
+        t[p + "norm1"] = vec(W)
+        t[p + "mix.q"] = mat(m["heads"] * m["dim"], W)
+        t[p + "mix.k"] = mat(m["kv_heads"] * m["dim"], W)
+        t[p + "mix.v"] = mat(m["kv_heads"] * m["vdim"], W)
+        t[p + "mix.q.norm"] = vec(m["heads"] * m["dim"])
+        t[p + "mix.k.norm"] = vec(m["kv_heads"] * m["dim"])
+        t[p + "mix.o"] = mat(W, m["heads"] * m["vdim"])
+        t[p + "ls1"] = vec(W)
+        if e.get("mlp"):
+            t[p + "mlp.gate"] = mat(e["mlp"]["ff"], W)
+            t[p + "mlp.up"] = mat(e["mlp"]["ff"], W)
+            t[p + "mlp.down"] = mat(W, e["mlp"]["ff"])
+            t[p + "ls2"] = vec(W)
+    return t

@@ -161,6 +161,10 @@ CONFIGS = {
     "mha_wide_values": dict(heads=3, kv_heads=3, dim=24, vdim=40, width=72, ff=50, window=6, keep=0, mult=1.0),
     "mqa_window_one": dict(heads=4, kv_heads=1, dim=16, vdim=16, window=1, keep=3, softcap_c=4.0),
     "window_longer_than_prompt": dict(window=500, keep=5, n_layers=2),
+    # every matrix tile-aligned: with BF16 weights the prompt pass runs on the tensor cores (fused gated epilogue included)
+    "tensor_core_tiles": dict(width=128, heads=4, kv_heads=4, dim=32, vdim=32, ff=256, n_layers=2),
+    # key / value projections too narrow for a tile: tensor-core and CUDA-core GEMMs mixed inside one layer
+    "mixed_tiles": dict(width=128, heads=4, kv_heads=1, dim=32, vdim=64, ff=128, n_layers=2, share={1: 0}),
 }
 
 

@@ -51,7 +51,7 @@ void nt_b200_gemv_dense(float* y0, float* y1, float* y2, const void* W0, const v
                         const float* x, int dtype, int epilogue, const float* row_scale, float alpha, void* stream);
 void nt_b200_gemm_dense(float* C, const float* A, const void* W, int dtype, int T, int N, int K, int epilogue, const float* row_scale, float alpha, void* stream);
 void nt_b200_attention_window(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int heads, int kv_heads,
-                              int dim, int vdim, int window, int keep, float scale, float softcap, void* stream);
+                              int dim, int vdim, int window, int keep, float scale, float softcap, int max_seq, void* stream);
 void nt_b200_qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
                               int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream);
 void nt_b200_glu_mul(float* out, const float* gate, const float* up, long long n, int gelu, void* stream);

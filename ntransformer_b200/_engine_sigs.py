@@ -60,7 +60,7 @@ ENGINE_SIGNATURES = {
     "nt_engine_generate_ids": (_i, [_vp, _vp, _i, _i, _f, _i, _f, _f, C.c_ulonglong, _vp, _i]),
     "nt_b200_gemv_dense": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _f, _vp]),
     "nt_b200_gemm_dense": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _f, _vp]),
-    "nt_b200_attention_window": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp]),
+    "nt_b200_attention_window": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp]),
     "nt_b200_qk_norm_kv_write": (None, [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "nt_b200_glu_mul": (None, [_vp, _vp, _vp, C.c_longlong, _i, _vp]),
     "nt_tp_unique_id": (_i, [_vp]),

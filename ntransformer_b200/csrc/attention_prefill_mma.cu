@@ -7,8 +7,13 @@
 // contractions on the warp-level tensor-core path (mma.sync m16n8k16, F32 accumulate) and an online softmax in
 // registers (flash-attention-2 data flow).  F32 operands are split into two F16 terms (q = hi + lo, p = hi + lo) so
 // the result keeps ~22 mantissa bits and stays within the 2e-5 tolerance of the oracle.
+//
+// The same kernel serves windowed attention (csrc/attention_window.cu's rule: key j visible from position p iff j <= p and
+// (p - j < window or j < keep)), optionally with soft-capped scores cap * tanh(s / cap) and a BF16 cache (BF: both MMAs take
+// BF16 operands, the splits are BF16 pairs): a query block then walks only the key tiles of the kept prefix and of its window.
 #include "kernels_internal.h"
 #include <cuda_fp16.h>
+#include <cuda_bf16.h>
 
 namespace nt { namespace b200 {
 
@@ -16,14 +21,29 @@ namespace {
 
 constexpr int BQ = 64, BKV = 64, PAD = 8;      // PAD halfs: row stride 272 B (hd 128) keeps LDS.32 / ldmatrix conflict-free
 
+template <bool BF>
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    if (BF)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 // (x, y) -> packed F16 hi pair and lo pair with x = hi + lo to ~2^-22
+template <bool BF>
 __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
+    if (BF) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(x, y);
+        const float2 fb = __bfloat1622float2(b);
+        const __nv_bfloat162 l = __floats2bfloat162_rn(x - fb.x, y - fb.y);
+        hi = *reinterpret_cast<const uint32_t*>(&b);
+        lo = *reinterpret_cast<const uint32_t*>(&l);
+        return;
+    }
     const __half2 h = __floats2half2_rn(x, y);
     const float2 f = __half22float2(h);
     hi = h2_bits(h);
@@ -33,11 +53,11 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int HD>
+template <int HD, bool BF>
 __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__ out, const float* __restrict__ Q,
                                                              const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                              int seq_len, int start_pos, int n_heads, int n_kv, int max_seq,
-                                                             float scale) {
+                                                             float scale, int window, int keep, float softcap) {
     constexpr int LD = HD + PAD, KS = HD / 16, NT = HD / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* sK = reinterpret_cast<__half*>(smem_raw);                 // [2][BKV][LD]
@@ -57,7 +77,7 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
             const int r = (i & 1) ? r1 : r0, c = ks * 16 + 2 * t + ((i & 2) ? 8 : 0);
             float2 v = make_float2(0.f, 0.f);
             if (r < seq_len) v = *reinterpret_cast<const float2*>(Q + ((size_t)r * n_heads + head) * HD + c);
-            split2(v.x, v.y, qhi[ks][i], qlo[ks][i]);
+            split2<BF>(v.x, v.y, qhi[ks][i], qlo[ks][i]);
         }
     }
     float o[NT][4];
@@ -66,13 +86,17 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     const int last_q = min(qb * BQ + BQ, seq_len) - 1;                // last valid query of the block
-    const int n_tiles = (start_pos + last_q) / BKV + 1;               // key tiles covering positions 0..start_pos+last_q
+    // key tiles: those of the kept prefix that lie before the block's window, then the window's (full causal: all from tile 0)
+    const int first_win = window > 0 ? max(0, start_pos + qb * BQ - window + 1) / BKV : 0;
+    const int n_keep = window > 0 ? min((keep + BKV - 1) / BKV, first_win) : 0;
+    const int n_tiles = n_keep + (start_pos + last_q) / BKV + 1 - first_win;
+    auto tile_of = [&](int j) { return j < n_keep ? j : first_win + (j - n_keep); };
 
     auto load_tile = [&](int j, int st) {
         constexpr int CH = HD / 8;                                    // 16-byte chunks per row
         for (int c = threadIdx.x; c < BKV * CH; c += 128) {
             const int row = c / CH, ch = c % CH;
-            const int key = min(j * BKV + row, max_seq - 1);          // rows past the cache are masked by causality anyway
+            const int key = min(tile_of(j) * BKV + row, max_seq - 1); // rows past the cache are masked by causality anyway
             const size_t src = ((size_t)key * n_kv + kvh) * HD + ch * 8;
             cp_async16(sK + ((size_t)st * BKV + row) * LD + ch * 8, kc + src);
             cp_async16(sV + ((size_t)st * BKV + row) * LD + ch * 8, vc + src);
@@ -103,12 +127,12 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
             for (int n = 0; n < 8; n++) {
                 const __half* kp = tK + (size_t)(n * 8 + g) * LD + ks * 16 + 2 * t;
                 const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kp), b1 = *reinterpret_cast<const uint32_t*>(kp + 8);
-                mma16816(s[n], qhi[ks], b0, b1);
-                mma16816(s[n], qlo[ks], b0, b1);
+                mma16816<BF>(s[n], qhi[ks], b0, b1);
+                mma16816<BF>(s[n], qlo[ks], b0, b1);
             }
         }
         // ---- scale, causal mask, online softmax ----
-        const int key0 = j * BKV;
+        const int key0 = tile_of(j) * BKV;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int n = 0; n < 8; n++) {
@@ -116,16 +140,22 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
             for (int i = 0; i < 4; i++) {
                 const int key = key0 + n * 8 + 2 * t + (i & 1);
                 const int p = (i & 2) ? p1 : p0;
-                const float v = key <= p ? s[n][i] * scale : -INFINITY;
+                const bool seen = key <= p && (window <= 0 || p - key < window || key < keep);
+                float v = s[n][i] * scale;
+                if (softcap > 0.f) v = softcap * (1.0f - 2.0f / (__expf(2.0f * v / softcap) + 1.0f));     // cap * tanh(v / cap)
+                v = seen ? v : -INFINITY;
                 s[n][i] = v;
                 if (i & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
             }
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);      // finite from tile 0 on: key 0 is visible to every row
+        // full causal: finite from tile 0 on (key 0 is visible to every row); with a window a row can find a whole tile masked
+        // before its first visible key: subtract 0 instead of -inf so every exponential is exp(-inf) = 0, not NaN
+        const float mr0 = fmaxf(m0, mx0), mr1 = fmaxf(m1, mx1);
+        const float mn0 = mr0 == -INFINITY ? 0.f : mr0, mn1 = mr1 == -INFINITY ? 0.f : mr1;
         const float a0 = __expf(m0 - mn0), a1 = __expf(m1 - mn1);
-        m0 = mn0; m1 = mn1;
+        m0 = mr0; m1 = mr1;
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int n = 0; n < 8; n++) {
@@ -141,10 +171,10 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
 #pragma unroll
         for (int kt = 0; kt < BKV / 16; kt++) {
             uint32_t phi[4], plo[4];
-            split2(s[2 * kt][0], s[2 * kt][1], phi[0], plo[0]);
-            split2(s[2 * kt][2], s[2 * kt][3], phi[1], plo[1]);
-            split2(s[2 * kt + 1][0], s[2 * kt + 1][1], phi[2], plo[2]);
-            split2(s[2 * kt + 1][2], s[2 * kt + 1][3], phi[3], plo[3]);
+            split2<BF>(s[2 * kt][0], s[2 * kt][1], phi[0], plo[0]);
+            split2<BF>(s[2 * kt][2], s[2 * kt][3], phi[1], plo[1]);
+            split2<BF>(s[2 * kt + 1][0], s[2 * kt + 1][1], phi[2], plo[2]);
+            split2<BF>(s[2 * kt + 1][2], s[2 * kt + 1][3], phi[3], plo[3]);
 #pragma unroll
             for (int np = 0; np < HD / 16; np++) {
                 // four 8x8 blocks of V^T: (keys +0..7 | +8..15) x (hd +0..7 | +8..15)
@@ -152,10 +182,10 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
                 uint32_t v0, v1, v2, v3;
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                              : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"((uint32_t)__cvta_generic_to_shared(vp)));
-                mma16816(o[2 * np], phi, v0, v1);
-                mma16816(o[2 * np], plo, v0, v1);
-                mma16816(o[2 * np + 1], phi, v2, v3);
-                mma16816(o[2 * np + 1], plo, v2, v3);
+                mma16816<BF>(o[2 * np], phi, v0, v1);
+                mma16816<BF>(o[2 * np], plo, v0, v1);
+                mma16816<BF>(o[2 * np + 1], phi, v2, v3);
+                mma16816<BF>(o[2 * np + 1], plo, v2, v3);
             }
         }
         __syncthreads();                                             // this stage is overwritten by the prefetch of tile j + 2
@@ -171,14 +201,15 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
     }
 }
 
-template <int HD>
+template <int HD, bool BF>
 void launch(float* out, const float* Q, const __half* kc, const __half* vc, int seq_len, int start_pos, int n_heads, int n_kv,
-            int max_seq, float scale, cudaStream_t s) {
+            int max_seq, float scale, int window, int keep, float softcap, cudaStream_t s) {
     const int smem = 2 * 2 * BKV * (HD + PAD) * (int)sizeof(__half);
     static unsigned long long configured = 0;      // bit per device id
-    opt_in_dynamic_smem(prefill_mma_kernel<HD>, (int)(smem), configured);
-    prefill_mma_kernel<HD><<<dim3((seq_len + BQ - 1) / BQ, n_heads), 128, smem, s>>>(out, Q, kc, vc, seq_len, start_pos, n_heads, n_kv,
-                                                                                    max_seq, scale);
+    opt_in_dynamic_smem(prefill_mma_kernel<HD, BF>, (int)(smem), configured);
+    prefill_mma_kernel<HD, BF><<<dim3((seq_len + BQ - 1) / BQ, n_heads), 128, smem, s>>>(out, Q, kc, vc, seq_len, start_pos, n_heads, n_kv,
+                                                                                        max_seq, scale, window, keep, softcap);
+    NT_LAUNCH_CHECK();
     count_launch();
 }
 
@@ -192,8 +223,20 @@ void attention_prefill_mma(float* out, const float* Q, const void* kc, const voi
                            int n_kv, int hd, int max_seq, float scale, cudaStream_t s) {
     const __half* k = static_cast<const __half*>(kc);
     const __half* v = static_cast<const __half*>(vc);
-    if (hd == 128) launch<128>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, s);
-    else launch<64>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, s);
+    if (hd == 128) launch<128, false>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, 0, 0, 0.f, s);
+    else launch<64, false>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, 0, 0, 0.f, s);
+}
+
+// Windowed / soft-capped form over a BF16 cache [max_seq][kv_heads][dim]: dim == vdim in {64, 128}, at least 16 queries.
+bool attention_window_mma_supported(int tokens, const WindowAttn& a, DType cache_dt) {
+    return cache_dt == DType::BF16 && a.dim == a.vdim && attention_prefill_mma_supported(tokens, a.heads, a.kv_heads, a.dim);
+}
+void attention_window_mma(float* out, const float* Q, const void* kc, const void* vc, int tokens, int p0, int max_seq, const WindowAttn& a,
+                          cudaStream_t s) {
+    const __half* k = static_cast<const __half*>(kc);       // 16-bit words either way; the BF instantiation reads them as BF16
+    const __half* v = static_cast<const __half*>(vc);
+    if (a.dim == 128) launch<128, true>(out, Q, k, v, tokens, p0, a.heads, a.kv_heads, max_seq, a.scale, a.window, a.keep, a.softcap, s);
+    else launch<64, true>(out, Q, k, v, tokens, p0, a.heads, a.kv_heads, max_seq, a.scale, a.window, a.keep, a.softcap, s);
 }
 
 }}  // namespace nt::b200

@@ -6,19 +6,21 @@
 // Keys and values come from the per-layer cache ([max_seq, kv_heads * dim] and [max_seq, kv_heads * vdim], F32 or BF16 storage):
 // the caller writes the step's rows first (qk_norm_kv_write), so a prompt portion, a whole prompt and a decoded token all take the
 // same kernel and see the same stored values.  Softmax, score and the weighted sum are F32.
-//   one CTA per (query token, head); its warps stride over the visible keys (the kept prefix, then the window) with a running
-//   (max, sum, acc) each, merged through shared memory at the end.
+//   one CTA per (query token, head); its warps stride over the visible keys (the kept prefix, then the window) in groups of 32
+//   with a running (max, sum, acc) each, merged through shared memory at the end.  Prompts over a BF16 cache with equal key and
+//   value width go to the tiled tensor-core form in attention_prefill_mma.cu instead.
 // Compiled WITHOUT --use_fast_math (tanhf / expf at full precision).
 #include "kernels_internal.h"
 #include "ring.cuh"
 #include <cuda_bf16.h>
 #include <cfloat>
+#include <cstdlib>
 
 namespace nt { namespace b200 {
 
 namespace {
 
-constexpr int AW_WARPS = 4;
+constexpr int AW_WARPS = 8;
 constexpr int AW_MAXV = 8;      // value elements per lane: vdim <= 256
 
 __device__ __forceinline__ float cache_ld(const float* p, size_t i) { return p[i]; }
@@ -26,13 +28,47 @@ __device__ __forceinline__ float cache_ld(const __nv_bfloat16* p, size_t i) { re
 __device__ __forceinline__ void cache_st(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void cache_st(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+// <q, row> for one cache row held by ONE lane (16-byte loads when the row is aligned)
+__device__ __forceinline__ float dot_row(const float* row, const float* qs, int dim, bool vec) {
+    float d = 0.f;
+    if (vec) {
+        for (int c = 0; c < dim; c += 4) {
+            const float4 k = *reinterpret_cast<const float4*>(row + c);
+            d = fmaf(qs[c], k.x, d); d = fmaf(qs[c + 1], k.y, d); d = fmaf(qs[c + 2], k.z, d); d = fmaf(qs[c + 3], k.w, d);
+        }
+    } else {
+        for (int c = 0; c < dim; c++) d = fmaf(qs[c], row[c], d);
+    }
+    return d;
+}
+__device__ __forceinline__ float dot_row(const __nv_bfloat16* row, const float* qs, int dim, bool vec) {
+    float d = 0.f;
+    if (vec) {
+        for (int c = 0; c < dim; c += 8) {
+            const uint4 k = *reinterpret_cast<const uint4*>(row + c);
+            const unsigned u[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                d = fmaf(qs[c + 2 * e], __uint_as_float(u[e] << 16), d);
+                d = fmaf(qs[c + 2 * e + 1], __uint_as_float(u[e] & 0xFFFF0000u), d);
+            }
+        }
+    } else {
+        for (int c = 0; c < dim; c++) d = fmaf(qs[c], cache_ld(row, c), d);
+    }
+    return d;
+}
+
+// Warps take groups of 32 visible keys.  Scoring is lane-per-key (each lane walks one key row against q in shared memory: no
+// cross-lane reduction per key); the group's maximum and the rescale are one warp reduction; the weighted value sum is
+// lane-per-channel (the 32 probabilities are broadcast one by one, value rows are read coalesced).
 template <typename KT>
 __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* __restrict__ out, const float* __restrict__ Q, const KT* __restrict__ kc,
                                                                          const KT* __restrict__ vc, const int* __restrict__ pos_dev, int p0,
                                                                          WindowAttn a) {
-    extern __shared__ float sm[];                 // q[dim] | per-warp acc[AW_WARPS][vdim] | m[AW_WARPS] | l[AW_WARPS]
+    extern __shared__ __align__(16) float sm[];   // q[dim rounded to 4] | per-warp acc[AW_WARPS][vdim] | m[AW_WARPS] | l[AW_WARPS]
     float* qs = sm;
-    float* accs = sm + a.dim;
+    float* accs = sm + ((a.dim + 3) & ~3);
     float* ms = accs + AW_WARPS * a.vdim;
     float* ls = ms + AW_WARPS;
     const int t = blockIdx.x, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
@@ -48,29 +84,43 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     const int n_first = min(a.keep, lo);
     const int n_keys = n_first + (pos - lo + 1);
     const size_t kstride = (size_t)a.kv_heads * a.dim, vstride = (size_t)a.kv_heads * a.vdim;
+    constexpr int PER16 = 16 / (int)sizeof(KT);
+    const bool vec = a.dim % PER16 == 0 && (reinterpret_cast<uintptr_t>(kc) & 15) == 0;      // every key row then starts on 16 bytes
     float m = -FLT_MAX, l = 0.f, acc[AW_MAXV];
 #pragma unroll
     for (int e = 0; e < AW_MAXV; e++) acc[e] = 0.f;
-    for (int n = warp; n < n_keys; n += AW_WARPS) {
-        const int j = n < n_first ? n : lo + (n - n_first);
-        const KT* kr = kc + (size_t)j * kstride + (size_t)g * a.dim;
-        float d = 0.f;
-        for (int i = lane; i < a.dim; i += 32) d = fmaf(qs[i], cache_ld(kr, i), d);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
-        float sc = d * a.scale;
-        if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
-        const float mn = fmaxf(m, sc);
-        const float corr = expf(m - mn), p = expf(sc - mn);
-        l = l * corr + p;
-        const KT* vr = vc + (size_t)j * vstride + (size_t)g * a.vdim;
-#pragma unroll
-        for (int e = 0; e < AW_MAXV; e++) {
-            const int i = lane + 32 * e;
-            if (i < a.vdim) acc[e] = fmaf(p, cache_ld(vr, i), acc[e] * corr);
+    for (int n0 = warp * 32; n0 < n_keys; n0 += AW_WARPS * 32) {
+        const int n = n0 + lane;
+        const bool valid = n < n_keys;
+        const int j = valid ? (n < n_first ? n : lo + (n - n_first)) : 0;
+        float sc = -FLT_MAX;
+        if (valid) {
+            sc = dot_row(kc + (size_t)j * kstride + (size_t)g * a.dim, qs, a.dim, vec) * a.scale;
+            if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
         }
+        float gmax = sc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, o));
+        const float mn = fmaxf(m, gmax);
+        const float corr = expf(m - mn), p = valid ? expf(sc - mn) : 0.f;
+        l = l * corr + p;                                   // per-lane partial sums, reduced once at the end
         m = mn;
+#pragma unroll
+        for (int e = 0; e < AW_MAXV; e++) acc[e] *= corr;
+        const int cnt = min(32, n_keys - n0);
+        for (int kk = 0; kk < cnt; kk++) {
+            const float pk = __shfl_sync(0xFFFFFFFFu, p, kk);
+            const int jk = __shfl_sync(0xFFFFFFFFu, j, kk);
+            const KT* vr = vc + (size_t)jk * vstride + (size_t)g * a.vdim;
+#pragma unroll
+            for (int e = 0; e < AW_MAXV; e++) {
+                const int i = lane + 32 * e;
+                if (i < a.vdim) acc[e] = fmaf(pk, cache_ld(vr, i), acc[e]);
+            }
+        }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, o);
     if (lane == 0) { ms[warp] = m; ls[warp] = l; }
 #pragma unroll
     for (int e = 0; e < AW_MAXV; e++) { const int i = lane + 32 * e; if (i < a.vdim) accs[warp * a.vdim + i] = acc[e]; }
@@ -131,12 +181,14 @@ __global__ void __launch_bounds__(256) qk_norm_kv_write_kernel(float* __restrict
 }  // namespace
 
 void attention_window(float* out, const float* Q, const void* kc, const void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0,
-                      const WindowAttn& a, cudaStream_t s) {
+                      int max_seq, const WindowAttn& a, cudaStream_t s) {
+    static const bool no_mma = getenv("NT_B200_NO_WINDOW_MMA") != nullptr;
+    if (!pos_dev && !no_mma && attention_window_mma_supported(tokens, a, cache_dt)) { attention_window_mma(out, Q, kc, vc, tokens, p0, max_seq, a, s); return; }
     NT_CHECK(a.vdim <= 32 * AW_MAXV, "attention_window: value heads wider than 256 are not covered");
     NT_CHECK(a.heads % a.kv_heads == 0, "attention_window: heads must be a multiple of kv_heads");
     NT_CHECK(cache_dt == DType::F32 || cache_dt == DType::BF16, "attention_window: F32 or BF16 cache");
     if (tokens <= 0) return;
-    const size_t smem = sizeof(float) * ((size_t)a.dim + (size_t)AW_WARPS * a.vdim + 2 * AW_WARPS);
+    const size_t smem = sizeof(float) * ((size_t)((a.dim + 3) & ~3) + (size_t)AW_WARPS * a.vdim + 2 * AW_WARPS);
     if (cache_dt == DType::F32)
         launch_k(attention_window_kernel<float>, dim3(tokens, a.heads), dim3(AW_WARPS * 32), smem, s, out, Q, static_cast<const float*>(kc),
                  static_cast<const float*>(vc), pos_dev, p0, a);

@@ -142,10 +142,10 @@ void nt_b200_gemm_dense(float* Cm, const float* A, const void* W, int dtype, int
     gemm_dense(Cm, A, W, (nt::DType)dtype, 0, T, N, K, (DenseEpilogue)epilogue, row_scale, alpha, static_cast<cudaStream_t>(stream));
 }
 void nt_b200_attention_window(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int heads, int kv_heads,
-                              int dim, int vdim, int window, int keep, float scale, float softcap, void* stream) {
+                              int dim, int vdim, int window, int keep, float scale, float softcap, int max_seq, void* stream) {
     WindowAttn a;
     a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.window = window; a.keep = keep; a.scale = scale; a.softcap = softcap;
-    attention_window(out, Q, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, a, static_cast<cudaStream_t>(stream));
+    attention_window(out, Q, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, max_seq, a, static_cast<cudaStream_t>(stream));
 }
 void nt_b200_qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
                               int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream) {

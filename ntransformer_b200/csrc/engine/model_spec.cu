@@ -203,7 +203,7 @@ void Model::step_body_spec(cudaStream_t s) {
         gemv_dense(qkv, 3, hidden, xnorm_, DENSE_STORE, nullptr, 1.f, s);
         qk_norm_kv_write(q_, k_, v_, L.q_norm, L.k_norm, cfg_.norm_eps, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, 1, pos_dev, 0, S.heads * S.dim,
                          S.kv_heads * S.dim, S.kv_heads * S.vdim, s);
-        attention_window(attn_, q_, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, 1, pos_dev, 0, attn_of(S), s);
+        attention_window(attn_, q_, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, 1, pos_dev, 0, cfg_.max_seq_len, attn_of(S), s);
         GemvMat o = mat_of(L.wo, hidden_);
         gemv_dense(&o, 1, S.heads * S.vdim, attn_, DENSE_SCALED_ADD, L.ls1, m, s);
         if (S.ff > 0) {
@@ -301,7 +301,7 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
             spec_gemm(pf_.v, hf, hs, L.wv, T, DENSE_STORE, nullptr, 1.f, s);
             qk_norm_kv_write(pf_.q, pf_.k, pf_.v, L.q_norm, L.k_norm, cfg_.norm_eps, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, T, nullptr, p0,
                              S.heads * S.dim, S.kv_heads * S.dim, S.kv_heads * S.vdim, s);
-            attention_window(pf_.attn, pf_.q, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, T, nullptr, p0, attn_of(S), s);
+            attention_window(pf_.attn, pf_.q, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, T, nullptr, p0, cfg_.max_seq_len, attn_of(S), s);
             const bool o_tc = spec_tc_ok(L.wo);
             if (o_tc) split_activations(pf_.ws, pf_.attn, T, S.heads * S.vdim, s, true);
             spec_gemm(pf_.x, pf_.attn, o_tc ? pf_.ws : nullptr, L.wo, T, DENSE_SCALED_ADD, L.ls1, m, s);

@@ -146,8 +146,13 @@ struct WindowAttn {
 };
 // Q [tokens, heads*dim] at positions base.. (base = *pos_dev when pos_dev is given, else p0); caches [max_seq, kv_heads*dim|vdim] of
 // cache_dt (F32 or BF16) that already hold the rows of these tokens; out [tokens, heads*vdim].
+// max_seq: rows of the cache (the tiled tensor-core form clamps its tile loads to it); prompts of >= 16 tokens over a BF16 cache
+// with dim == vdim in {64, 128} take attention_prefill_mma.cu's tiles, everything else one CTA per (token, head).
 void attention_window(float* out, const float* Q, const void* kc, const void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0,
-                      const WindowAttn& a, cudaStream_t s);
+                      int max_seq, const WindowAttn& a, cudaStream_t s);
+bool attention_window_mma_supported(int tokens, const WindowAttn& a, DType cache_dt);
+void attention_window_mma(float* out, const float* Q, const void* kc, const void* vc, int tokens, int p0, int max_seq, const WindowAttn& a,
+                          cudaStream_t s);
 // Whole-projection RMS norm of the query rows (in place) and key rows (gains may be null: no norm), key/value rows -> cache rows base + t.
 void qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
                       DType cache_dt, int tokens, const int* pos_dev, int p0, int qdim, int kdim, int vdim, cudaStream_t s);

@@ -90,7 +90,8 @@ def run_window_attention(q, k, v, heads, kv, dim, vdim, window, keep, scale, cap
     Q = dev(q[p0:])
     out = torch.zeros(S - p0, heads * vdim, device="cuda")
     lib().nt_b200_attention_window(out.data_ptr(), Q.data_ptr(), kc.data_ptr(), vc.data_ptr(), int(cache_dt), S - p0, p0, heads, kv, dim, vdim, window, keep,
-                                   scale, cap, stream())
+                                   scale, cap, max_seq, stream())
+    torch.cuda.synchronize()
     return out.cpu().numpy()
 
 
@@ -108,19 +109,39 @@ def test_attention_window_against_oracle(heads, kv, dim, vdim, window, keep):
     assert np.abs(got - ref[3:]).max() < 0.05
 
 
-def test_attention_window_edges_show():
+def bf16_round(a):
+    return torch.from_numpy(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+
+
+@pytest.mark.parametrize("heads,kv,dim,window,keep", [(4, 2, 64, 70, 3), (2, 2, 128, 64, 66), (2, 1, 64, 1, 0), (2, 1, 64, 300, 130)])
+def test_attention_window_tiled_tensor_core_form(heads, kv, dim, window, keep):
+    """Prompt portions of >= 16 tokens over a BF16 cache with equal key / value width take the tiled mma form: windows and kept
+    prefixes that straddle its 64-key tiles, portions that start inside a tile."""
+    rng = np.random.default_rng(window)
+    S = 200
+    q = rng.standard_normal((S, heads * dim)); k = bf16_round(rng.standard_normal((S, kv * dim))); v = bf16_round(rng.standard_normal((S, kv * dim)))
+    scale, cap = 1.2 / math.sqrt(dim), 8.0
+    ref = O.window_attention(q, k, v, heads, kv, dim, dim, scale, cap, window, keep)
+    for p0 in (0, 50, 131, S - 16):
+        got = run_window_attention(q, k, v, heads, kv, dim, dim, window, keep, scale, cap, p0, cache_dt=DType.BF16, max_seq=S + 7)
+        np.testing.assert_allclose(got, ref[p0:], rtol=2e-3, atol=2e-3)
+    one = run_window_attention(q, k, v, heads, kv, dim, dim, window, keep, scale, cap, S - 1, cache_dt=DType.BF16)      # one token: the per-token form
+    np.testing.assert_allclose(one, ref[S - 1:], rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("dim,vdim,cache_dt,S", [(16, 8, DType.F32, 40), (64, 64, DType.BF16, 150)])
+def test_attention_window_edges_show(dim, vdim, cache_dt, S):
     """One key gets a score far above the rest and a marked value: the output tells whether the query saw it."""
-    heads, kv, dim, vdim, window, keep = 2, 1, 16, 8, 6, 3
-    S = 40
+    heads, kv, window, keep = 2, 1, 6, 3
     rng = np.random.default_rng(3)
-    for i in (S - 1, 25):
+    for i in (S - 1, S - 15):
         for j, seen in ((i - window + 1, True), (i - window, False), (keep - 1, True), (keep, False), (0, True), (i, True), (i - 1, True)):
             q = rng.standard_normal((S, heads * dim)) * 0.05; k = rng.standard_normal((S, kv * dim)) * 0.05; v = rng.standard_normal((S, kv * vdim)) * 0.01
             unit = np.zeros(dim); unit[5] = 1.0
             q[i] = np.tile(unit * 10.0, heads); k[j] = unit * 10.0
             v[j] = 0.0; v[j, 3] = 1.0
             for p0 in (0, i):                    # inside a prompt portion, and as a token decoded alone
-                out = run_window_attention(q[:i + 1], k[:i + 1], v[:i + 1], heads, kv, dim, vdim, window, keep, 1.0, 30.0, p0, max_seq=64)
+                out = run_window_attention(q[:i + 1], k[:i + 1], v[:i + 1], heads, kv, dim, vdim, window, keep, 1.0, 30.0, p0, cache_dt=cache_dt, max_seq=S + 24)
                 mark = out[i - p0].reshape(heads, vdim)[:, 3]
                 assert (mark > 0.99).all() if seen else (np.abs(mark) < 0.05).all(), (i, j, p0, mark)
 
@@ -164,6 +185,7 @@ CONFIGS = {
     # every matrix tile-aligned: with BF16 weights the prompt pass runs on the tensor cores (fused gated epilogue included)
     "tensor_core_tiles": dict(width=128, heads=4, kv_heads=4, dim=32, vdim=32, ff=256, n_layers=2),
     # key / value projections too narrow for a tile: tensor-core and CUDA-core GEMMs mixed inside one layer
+    "tiled_attention": dict(width=64, heads=2, kv_heads=1, dim=64, vdim=64, ff=64, n_layers=2, window=20, keep=3),
     "mixed_tiles": dict(width=128, heads=4, kv_heads=1, dim=32, vdim=64, ff=128, n_layers=2, share={1: 0}),
 }
 

@@ -7,20 +7,24 @@
 // the caller writes the step's rows first (qk_norm_kv_write), so a prompt portion, a whole prompt and a decoded token all take the
 // same kernel and see the same stored values.  Softmax, score and the weighted sum are F32.
 //   one CTA per (query token, head); its warps stride over the visible keys (the kept prefix, then the window) in groups of 32
-//   with a running (max, sum, acc) each, merged through shared memory at the end.  Prompts over a BF16 cache with equal key and
+//   with a running (max, sum, acc) each, merged through shared memory at the end; for a single decoded token the keys of a head
+//   are further split over the CTAs of a thread-block cluster and merged through the leader's distributed shared memory.  Prompts over a BF16 cache with equal key and
 //   value width go to the tiled tensor-core form in attention_prefill_mma.cu instead.
 // Compiled WITHOUT --use_fast_math (tanhf / expf at full precision).
 #include "kernels_internal.h"
 #include "ring.cuh"
 #include <cuda_bf16.h>
+#include <cooperative_groups.h>
 #include <cfloat>
 #include <cstdlib>
+#include <algorithm>
 
 namespace nt { namespace b200 {
 
 namespace {
 
 constexpr int AW_WARPS = 8;
+constexpr int AW_MAX_SPLITS = 8;   // CTAs of one cluster sharing a (token, head): portable cluster size
 constexpr int AW_MAXV = 8;      // value elements per lane: vdim <= 256
 
 __device__ __forceinline__ float cache_ld(const float* p, size_t i) { return p[i]; }
@@ -32,6 +36,7 @@ __device__ __forceinline__ void cache_st(__nv_bfloat16* p, size_t i, float v) { 
 __device__ __forceinline__ float dot_row(const float* row, const float* qs, int dim, bool vec) {
     float d = 0.f;
     if (vec) {
+#pragma unroll 8
         for (int c = 0; c < dim; c += 4) {
             const float4 k = *reinterpret_cast<const float4*>(row + c);
             d = fmaf(qs[c], k.x, d); d = fmaf(qs[c + 1], k.y, d); d = fmaf(qs[c + 2], k.z, d); d = fmaf(qs[c + 3], k.w, d);
@@ -44,6 +49,7 @@ __device__ __forceinline__ float dot_row(const float* row, const float* qs, int 
 __device__ __forceinline__ float dot_row(const __nv_bfloat16* row, const float* qs, int dim, bool vec) {
     float d = 0.f;
     if (vec) {
+#pragma unroll 8
         for (int c = 0; c < dim; c += 8) {
             const uint4 k = *reinterpret_cast<const uint4*>(row + c);
             const unsigned u[4] = {k.x, k.y, k.z, k.w};
@@ -66,11 +72,16 @@ template <typename KT>
 __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* __restrict__ out, const float* __restrict__ Q, const KT* __restrict__ kc,
                                                                          const KT* __restrict__ vc, const int* __restrict__ pos_dev, int p0,
                                                                          WindowAttn a) {
-    extern __shared__ __align__(16) float sm[];   // q[dim rounded to 4] | per-warp acc[AW_WARPS][vdim] | m[AW_WARPS] | l[AW_WARPS]
+    // q[dim rounded to 4] | per-warp acc[AW_WARPS][vdim] | m[AW_WARPS] | l[AW_WARPS] | per-CTA partials [splits][vdim + 2] (leader's copy is used)
+    extern __shared__ __align__(16) float sm[];
     float* qs = sm;
     float* accs = sm + ((a.dim + 3) & ~3);
     float* ms = accs + AW_WARPS * a.vdim;
     float* ls = ms + AW_WARPS;
+    float* part = ls + AW_WARPS;
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int splits = gridDim.z, rank = blockIdx.z;       // the cluster spans z: its CTAs share the (token, head) and split the keys
     const int t = blockIdx.x, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -79,6 +90,7 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     const float* q = Q + (size_t)t * a.heads * a.dim + (size_t)h * a.dim;
     for (int i = threadIdx.x; i < a.dim; i += AW_WARPS * 32) qs[i] = q[i];
     __syncthreads();
+    if (splits > 1) cluster.sync();                          // every CTA of the cluster is resident before anyone writes into a peer's shared memory
     // visible keys: [0, n_first) and [lo, pos]
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int n_first = min(a.keep, lo);
@@ -89,7 +101,7 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     float m = -FLT_MAX, l = 0.f, acc[AW_MAXV];
 #pragma unroll
     for (int e = 0; e < AW_MAXV; e++) acc[e] = 0.f;
-    for (int n0 = warp * 32; n0 < n_keys; n0 += AW_WARPS * 32) {
+    for (int n0 = (rank * AW_WARPS + warp) * 32; n0 < n_keys; n0 += splits * AW_WARPS * 32) {
         const int n = n0 + lane;
         const bool valid = n < n_keys;
         const int j = valid ? (n < n_first ? n : lo + (n - n_first)) : 0;
@@ -107,8 +119,10 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
         m = mn;
 #pragma unroll
         for (int e = 0; e < AW_MAXV; e++) acc[e] *= corr;
-        const int cnt = min(32, n_keys - n0);
-        for (int kk = 0; kk < cnt; kk++) {
+        // all 32 slots: lanes past the last key carry p == 0 and row 0, so the trip count is fixed and the loads of several
+        // keys are in flight together
+#pragma unroll 8
+        for (int kk = 0; kk < 32; kk++) {
             const float pk = __shfl_sync(0xFFFFFFFFu, p, kk);
             const int jk = __shfl_sync(0xFFFFFFFFu, j, kk);
             const KT* vr = vc + (size_t)jk * vstride + (size_t)g * a.vdim;
@@ -130,10 +144,33 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     float L = 0.f;
     for (int w = 0; w < AW_WARPS; w++) L += ls[w] * expf(ms[w] - M);
     float* o = out + (size_t)t * a.heads * a.vdim + (size_t)h * a.vdim;
+    if (splits == 1) {
+        for (int i = threadIdx.x; i < a.vdim; i += AW_WARPS * 32) {
+            float v = 0.f;
+            for (int w = 0; w < AW_WARPS; w++) v += accs[w * a.vdim + i] * expf(ms[w] - M);
+            o[i] = v / L;
+        }
+        return;
+    }
+    // this CTA's (max, sum, unnormalised vector) goes into slot `rank` of the leader's shared memory (distributed shared memory),
+    // the cluster barrier orders the writes before the leader's reads, the leader merges the slots
+    float* dst = cluster.map_shared_rank(part, 0) + (size_t)rank * (a.vdim + 2);
     for (int i = threadIdx.x; i < a.vdim; i += AW_WARPS * 32) {
         float v = 0.f;
         for (int w = 0; w < AW_WARPS; w++) v += accs[w * a.vdim + i] * expf(ms[w] - M);
-        o[i] = v / L;
+        dst[2 + i] = v;
+    }
+    if (threadIdx.x == 0) { dst[0] = M; dst[1] = L; }
+    cluster.sync();
+    if (rank != 0) return;
+    float MM = -FLT_MAX;
+    for (int r = 0; r < splits; r++) MM = fmaxf(MM, part[(size_t)r * (a.vdim + 2)]);
+    float LL = 0.f;
+    for (int r = 0; r < splits; r++) LL += part[(size_t)r * (a.vdim + 2) + 1] * expf(part[(size_t)r * (a.vdim + 2)] - MM);
+    for (int i = threadIdx.x; i < a.vdim; i += AW_WARPS * 32) {
+        float v = 0.f;
+        for (int r = 0; r < splits; r++) v += part[(size_t)r * (a.vdim + 2) + 2 + i] * expf(part[(size_t)r * (a.vdim + 2)] - MM);
+        o[i] = v / LL;
     }
 }
 
@@ -188,13 +225,24 @@ void attention_window(float* out, const float* Q, const void* kc, const void* vc
     NT_CHECK(a.heads % a.kv_heads == 0, "attention_window: heads must be a multiple of kv_heads");
     NT_CHECK(cache_dt == DType::F32 || cache_dt == DType::BF16, "attention_window: F32 or BF16 cache");
     if (tokens <= 0) return;
-    const size_t smem = sizeof(float) * ((size_t)((a.dim + 3) & ~3) + (size_t)AW_WARPS * a.vdim + 2 * AW_WARPS);
+    // A single decoded token has only `heads` CTAs: split each head's keys over a thread-block cluster (one CTA per ~256 keys of
+    // the longest visible range), merged through the leader's shared memory.  Prompt portions have CTAs enough without it.
+    const int longest = a.window > 0 ? std::min(max_seq, a.window + a.keep) : max_seq;
+    const int splits = tokens == 1 ? std::max(1, std::min(AW_MAX_SPLITS, (longest + 255) / 256)) : 1;
+    const size_t smem = sizeof(float) * ((size_t)((a.dim + 3) & ~3) + (size_t)AW_WARPS * a.vdim + 2 * AW_WARPS + (size_t)splits * (a.vdim + 2));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(tokens, a.heads, splits); cfg.blockDim = dim3(AW_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    at[1].id = cudaLaunchAttributeClusterDimension;
+    at[1].val.clusterDim.x = 1; at[1].val.clusterDim.y = 1; at[1].val.clusterDim.z = (unsigned)splits;
+    cfg.attrs = at; cfg.numAttrs = 2;
     if (cache_dt == DType::F32)
-        launch_k(attention_window_kernel<float>, dim3(tokens, a.heads), dim3(AW_WARPS * 32), smem, s, out, Q, static_cast<const float*>(kc),
-                 static_cast<const float*>(vc), pos_dev, p0, a);
+        NT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, attention_window_kernel<float>, out, Q, static_cast<const float*>(kc), static_cast<const float*>(vc), pos_dev, p0, a));
     else
-        launch_k(attention_window_kernel<__nv_bfloat16>, dim3(tokens, a.heads), dim3(AW_WARPS * 32), smem, s, out, Q,
-                 static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), pos_dev, p0, a);
+        NT_CUDA_CHECK(cudaLaunchKernelEx(&cfg, attention_window_kernel<__nv_bfloat16>, out, Q, static_cast<const __nv_bfloat16*>(kc),
+                                         static_cast<const __nv_bfloat16*>(vc), pos_dev, p0, a));
     count_launch();
 }
 

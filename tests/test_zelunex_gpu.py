@@ -129,6 +129,21 @@ def test_attention_window_tiled_tensor_core_form(heads, kv, dim, window, keep):
     np.testing.assert_allclose(one, ref[S - 1:], rtol=2e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("window,keep,S", [(600, 5, 700), (0 + 300, 300, 1500), (2000, 0, 900)])
+def test_decoded_token_over_a_long_window_splits_across_a_cluster(window, keep, S):
+    """One token against hundreds of keys: the head's keys are split over several CTAs and merged; kept prefix and window far apart."""
+    heads, kv, dim, vdim = 4, 2, 32, 48
+    rng = np.random.default_rng(S)
+    q = rng.standard_normal((S, heads * dim)); k = rng.standard_normal((S, kv * dim)); v = rng.standard_normal((S, kv * vdim))
+    scale, cap = 1.0 / math.sqrt(dim), 10.0
+    ref = O.window_attention_row(q[S - 1], k, v, S - 1, heads, kv, dim, vdim, scale, cap, window, keep)
+    got = run_window_attention(q, k, v, heads, kv, dim, vdim, window, keep, scale, cap, S - 1, max_seq=S + 100)
+    np.testing.assert_allclose(got[0], ref, rtol=2e-5, atol=2e-5)
+    got = run_window_attention(q, bf16_round(k), bf16_round(v), heads, kv, dim, vdim, window, keep, scale, cap, S - 1, cache_dt=DType.BF16, max_seq=S + 100)
+    ref = O.window_attention_row(q[S - 1], bf16_round(k), bf16_round(v), S - 1, heads, kv, dim, vdim, scale, cap, window, keep)
+    np.testing.assert_allclose(got[0], ref, rtol=2e-5, atol=2e-5)
+
+
 @pytest.mark.parametrize("dim,vdim,cache_dt,S", [(16, 8, DType.F32, 40), (64, 64, DType.BF16, 150)])
 def test_attention_window_edges_show(dim, vdim, cache_dt, S):
     """One key gets a score far above the rest and a marked value: the output tells whether the query saw it."""

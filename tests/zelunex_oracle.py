@@ -53,6 +53,19 @@ def window_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, heads: int, kv
     return out
 
 
+def window_attention_row(q_i: np.ndarray, k: np.ndarray, v: np.ndarray, i: int, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                         cap: float, window: int, keep: int) -> np.ndarray:
+    """The same for the single query at position i (long contexts, where the all-pairs loop above is too slow)."""
+    js = np.array([j for j in range(i + 1) if visible(i, j, window, keep)])
+    out = np.zeros(heads * vdim)
+    for h in range(heads):
+        g = h // (heads // kv_heads)
+        s = cap * np.tanh(scale * (k[js, g * dim:(g + 1) * dim] @ q_i[h * dim:(h + 1) * dim]) / cap)
+        p = np.exp(s - s.max())
+        out[h * vdim:(h + 1) * vdim] = (p / p.sum()) @ v[js, g * vdim:(g + 1) * vdim]
+    return out
+
+
 def mixer_attention(h: np.ndarray, W: dict, pre: str, mc: dict, eps: float) -> np.ndarray:
     q = h @ W[pre + "mix.q"].T
     k = h @ W[pre + "mix.k"].T

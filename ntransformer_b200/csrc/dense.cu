@@ -2,7 +2,7 @@
 // elementwise pieces of the layer-spec model families (engine/layer_spec.h).
 //
 //   gemv_dense   decode: up to 3 matrices share one activation vector staged once per CTA in shared memory; a warp streams one
-//                output row with 16-byte loads; epilogues fuse the residual (+ per-channel gain) and the gated activations, so a
+//                output row with 16-byte loads; the prologue can RMS-normalise the staged vector; epilogues fuse the residual (+ per-channel gain) and the gated activations, so a
 //                decode step needs no separate add / scale / activation launch.
 //   gemm_dense   prompt tokens on CUDA cores: 64x64x16 tiles, 4x4 outputs per thread, true FP32 FMA.  It serves the exact
 //                32-bit mode and shapes the tcgen05 tiles of prefill_gemm.cu do not cover (rows % 128, cols % 64).
@@ -101,12 +101,28 @@ __device__ __forceinline__ float dense_row_dot(const unsigned char* row, const f
 
 template <typename T>
 __global__ void __launch_bounds__(DV_WARPS * 32) gemv_dense_kernel(DenseMats m, const float* __restrict__ x, int K, int ep,
-                                                                   const float* __restrict__ row_scale, float alpha, int vec) {
+                                                                   const float* __restrict__ row_scale, float alpha, int vec,
+                                                                   const float* __restrict__ norm_w, float eps) {
     extern __shared__ __align__(16) float xs[];
+    __shared__ float red[DV_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();
-    for (int i = threadIdx.x; i < K; i += DV_WARPS * 32) xs[i] = x[i];
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < K; i += DV_WARPS * 32) { const float v = x[i]; xs[i] = v; ss = fmaf(v, v, ss); }
+    if (norm_w) {
+        // RMS norm of the staged vector: every CTA sums the squares in the same order, so all CTAs (and every launch that reads the
+        // same x) derive the bit-identical normalised vector
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < DV_WARPS; w++) tot += red[w];
+        const float inv = 1.0f / sqrtf(tot / (float)K + eps);
+        for (int i = threadIdx.x; i < K; i += DV_WARPS * 32) xs[i] = xs[i] * inv * norm_w[i];
+    }
     __syncthreads();
     const bool glu = ep == DENSE_SWIGLU || ep == DENSE_GEGLU;
     const int total = glu ? m.out[0] : m.out[0] + (m.n > 1 ? m.out[1] : 0) + (m.n > 2 ? m.out[2] : 0);
@@ -194,7 +210,8 @@ __global__ void to_f32_kernel(float* __restrict__ out, const T* __restrict__ in,
 
 bool dense_dtype(DType dt) { return dt == DType::F32 || dt == DType::F16 || dt == DType::BF16; }
 
-void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s) {
+void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s,
+                const float* norm_w, float eps) {
     NT_CHECK(n_mat >= 1 && n_mat <= 3, "gemv_dense: 1..3 matrices");
     const bool glu = ep == DENSE_SWIGLU || ep == DENSE_GEGLU;
     NT_CHECK(!glu || (n_mat == 2 && mats[0].out == mats[1].out), "gemv_dense: a gated epilogue takes two matrices of equal height");
@@ -219,7 +236,7 @@ void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpil
     const int resident = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(220 * 1024) / (smem + 1024))) * 148;
     grid = std::min(grid, resident);
 #define NT_DV(TY) { static unsigned long long done = 0; if (smem > 48 * 1024) opt_in_dynamic_smem(gemv_dense_kernel<TY>, 200 * 1024, done); \
-                    launch_k(gemv_dense_kernel<TY>, dim3(grid), dim3(DV_WARPS * 32), smem, s, m, x, K, (int)ep, row_scale, alpha, vec); }
+                    launch_k(gemv_dense_kernel<TY>, dim3(grid), dim3(DV_WARPS * 32), smem, s, m, x, K, (int)ep, row_scale, alpha, vec, norm_w, eps); }
     if (dt == DType::F32) NT_DV(float) else if (dt == DType::F16) NT_DV(__half) else NT_DV(__nv_bfloat16)
 #undef NT_DV
     count_launch();

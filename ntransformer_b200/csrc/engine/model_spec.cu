@@ -7,9 +7,9 @@
 // Arithmetic: the residual stream, norms, softmax and every accumulation are F32.  Weights stay in their stored dtype (BF16)
 // and are widened in registers, or — exact 32-bit mode — are widened once at load.  The cache stores BF16 (F32 in exact mode).
 //
-// Launches per layer and decoded token (6):  [RMS norm]  [q/k/v GEMV, one launch]  [q/k norm + cache write]  [window attention]
-//   [o GEMV: x += m * ls1 * .]  [gate/up GEMV + GELU gate]  [down GEMV: x += m * ls2 * .]   — every residual update, gain and
-//   activation lives in a GEMV epilogue.  Both branches read the same normed vector, so the order of the two updates is free.
+// Launches per layer and decoded token (6):  [RMS norm + q/k/v GEMV, one launch]  [q/k norm + cache write]  [window attention]
+//   [RMS norm + gate/up GEMV + GELU gate]  [o GEMV: x += m * ls1 * .]  [down GEMV: x += m * ls2 * .]   — the block norm lives in
+//   the GEMV prologues, every residual update, gain and activation in a GEMV epilogue.
 #include "model.h"
 #include "safetensors.h"
 
@@ -198,17 +198,20 @@ void Model::step_body_spec(cudaStream_t s) {
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerSpec& S = cfg_.layers[(size_t)i];
         const LayerWeights& L = layer_weights(i);
-        rmsnorm(xnorm_, hidden_, L.attn_norm, 1, hidden, cfg_.norm_eps, s);
+        // Both branches read norm(x) of the x the layer started from.  The q/k/v and the gate/up launches each normalise hidden_ in
+        // their prologue (bit-identical results), and both run before the first epilogue that updates hidden_.
         GemvMat qkv[3] = {mat_of(L.wq, q_), mat_of(L.wk, k_), mat_of(L.wv, v_)};
-        gemv_dense(qkv, 3, hidden, xnorm_, DENSE_STORE, nullptr, 1.f, s);
+        gemv_dense(qkv, 3, hidden, hidden_, DENSE_STORE, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps);
         qk_norm_kv_write(q_, k_, v_, L.q_norm, L.k_norm, cfg_.norm_eps, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, 1, pos_dev, 0, S.heads * S.dim,
                          S.kv_heads * S.dim, S.kv_heads * S.vdim, s);
         attention_window(attn_, q_, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, 1, pos_dev, 0, cfg_.max_seq_len, attn_of(S), s);
+        if (S.ff > 0) {
+            GemvMat gu[2] = {mat_of(L.gate, act_), mat_of(L.up, nullptr)};
+            gemv_dense(gu, 2, hidden, hidden_, S.act == GluAct::GELU_TANH ? DENSE_GEGLU : DENSE_SWIGLU, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps);
+        }
         GemvMat o = mat_of(L.wo, hidden_);
         gemv_dense(&o, 1, S.heads * S.vdim, attn_, DENSE_SCALED_ADD, L.ls1, m, s);
         if (S.ff > 0) {
-            GemvMat gu[2] = {mat_of(L.gate, act_), mat_of(L.up, nullptr)};
-            gemv_dense(gu, 2, hidden, xnorm_, S.act == GluAct::GELU_TANH ? DENSE_GEGLU : DENSE_SWIGLU, nullptr, 1.f, s);
             GemvMat d = mat_of(L.down, hidden_);
             gemv_dense(&d, 1, S.ff, act_, DENSE_SCALED_ADD, L.ls2, m, s);
         }
@@ -216,9 +219,8 @@ void Model::step_body_spec(cudaStream_t s) {
 }
 
 void Model::step_head_spec(cudaStream_t s) {
-    rmsnorm(xnorm_, hidden_, out_norm_, 1, cfg_.hidden_size, cfg_.norm_eps, s);
     GemvMat h = mat_of(head_, logits_);
-    gemv_dense(&h, 1, cfg_.hidden_size, xnorm_, DENSE_STORE, nullptr, 1.f, s);
+    gemv_dense(&h, 1, cfg_.hidden_size, hidden_, DENSE_STORE, nullptr, 1.f, s, out_norm_, cfg_.norm_eps);       // final norm in the prologue
 }
 
 void Model::ensure_prefill_buffers_spec(int tokens) {

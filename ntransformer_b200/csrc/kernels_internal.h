@@ -132,7 +132,9 @@ enum DenseEpilogue { DENSE_STORE = 0, DENSE_ADD = 1, DENSE_SCALED_ADD = 2 /* y[r
                      DENSE_SWIGLU = 3 /* y0 = silu(W0.x) * (W1.x) */, DENSE_GEGLU = 4 /* y0 = gelu_tanh(W0.x) * (W1.x) */ };
 bool dense_dtype(DType dt);
 // Up to 3 matrices of one dense dtype sharing the activation vector x[K] (GemvMat::y: each matrix's output rows).
-void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s);
+// norm_w: the kernel's prologue first replaces x by x / sqrt(mean(x^2) + eps) * norm_w (the block's RMS norm, recomputed per CTA).
+void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s,
+                const float* norm_w = nullptr, float eps = 0.f);
 // C[T,N] (ep)= A[T,K] . W[N,K]^T in true FP32 on CUDA cores (store / add / scaled-add; row_scale indexes N).
 void gemm_dense(float* C, const float* A, const void* W, DType dt, size_t row_pitch, int T, int N, int K, DenseEpilogue ep,
                 const float* row_scale, float alpha, cudaStream_t s);

@@ -91,7 +91,7 @@ def bytes_per_token(cfg: LlamaConfig, mix: str, ctx: int, tp_size: int = 1) -> i
 
 # ---- Zelunex (layer-spec family, model folders): synthetic configurations and random device weights for benchmarks ----
 def zelunex_config(vocab=32000, width=4096, n_layers=4, heads=32, kv_heads=8, dim=128, vdim=128, ff=14336, window=1024, keep_first=4,
-                   softcap=30.0, eps=1e-5, residual_mult=0.7, share=None):
+                   softcap=30.0, eps=1e-5, residual_mult=0.5, share=None):
     """The family's config.json as a dict.  share: {layer: earlier layer whose tensors it reads}."""
     share = share or {}
     layers = []

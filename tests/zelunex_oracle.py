@@ -103,7 +103,7 @@ def forward(cfg: dict, W: dict, tokens, return_layers: bool = False):
 
 
 def random_model(rng: np.random.Generator, *, vocab=96, width=64, n_layers=3, heads=4, kv_heads=2, dim=32, vdim=16, ff=96, window=8, keep=2,
-                 softcap_c=15.0, scale=None, eps=1e-3, mult=0.6, share=None, no_mlp=()):
+                 softcap_c=15.0, scale=None, eps=4e-3, mult=0.6, share=None, no_mlp=()):
     """A small random configuration + weights (bf16-representable values). share: {layer: source layer}."""
     import torch
 

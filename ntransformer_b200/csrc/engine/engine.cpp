@@ -38,6 +38,10 @@ bool Engine::load_tp(const std::string& path, int max_context, int tp_rank, int 
 
 std::string Engine::generate(const std::string& prompt, const GenerateConfig& cfg, TokenCallback cb) {
     std::string out;
+    if (model_.vocab().tokens.empty()) {          // model folders carry no vocabulary
+        fprintf(stderr, "Error: this model has no vocabulary; give the prompt as token ids (--ids, Engine::generate_ids)\n");
+        return out;
+    }
     generate_ids(tok_.encode(prompt, true), cfg, [&](int id) {
         const std::string piece = tok_.decode_token(id);
         out += piece;

@@ -292,8 +292,9 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
             const LayerWeights& L = layer_weights(i);
             // the block's normed input feeds q, k, v, gate and up: as FP32 rows, as a BF16 split, or both, by what those matrices take
             bool h_f32 = false, h_split = false;
-            for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.gate, &L.up})
-                if (w->ptr && (w == &L.wq || w == &L.wk || w == &L.wv || S.ff > 0)) (spec_tc_ok(*w) ? h_split : h_f32) = true;
+            auto reads_h = [&](const Weight& w) { if (spec_tc_ok(w)) h_split = true; else h_f32 = true; };
+            reads_h(L.wq); reads_h(L.wk); reads_h(L.wv);
+            if (S.ff > 0) { reads_h(L.gate); reads_h(L.up); }
             if (h_f32) rmsnorm(pf_.h, pf_.x, L.attn_norm, T, hidden, cfg_.norm_eps, s);
             if (h_split) rmsnorm_split(pf_.hws, pf_.x, L.attn_norm, T, hidden, cfg_.norm_eps, s, true);
             const float* hf = h_f32 ? pf_.h : nullptr;

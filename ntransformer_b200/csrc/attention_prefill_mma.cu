@@ -229,7 +229,7 @@ void attention_prefill_mma(float* out, const float* Q, const void* kc, const voi
 
 // Windowed / soft-capped form over a BF16 cache [max_seq][kv_heads][dim]: dim == vdim in {64, 128}, at least 16 queries.
 bool attention_window_mma_supported(int tokens, const WindowAttn& a, DType cache_dt) {
-    return cache_dt == DType::BF16 && a.dim == a.vdim && attention_prefill_mma_supported(tokens, a.heads, a.kv_heads, a.dim);
+    return cache_dt == DType::BF16 && a.dim == a.vdim && a.maps == 1 && a.chunk == 0 && attention_prefill_mma_supported(tokens, a.heads, a.kv_heads, a.dim);
 }
 void attention_window_mma(float* out, const float* Q, const void* kc, const void* vc, int tokens, int p0, int max_seq, const WindowAttn& a,
                           cudaStream_t s) {

@@ -82,20 +82,21 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int splits = gridDim.z, rank = blockIdx.z;       // the cluster spans z: its CTAs share the (token, head) and split the keys
-    const int t = blockIdx.x, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+    // blockIdx.y walks (head, map): map mp of head h scores against map mp of key head g and sums the head's one value row
+    const int t = blockIdx.x, hm = blockIdx.y, h = hm / a.maps, mp = hm % a.maps, g = h / (a.heads / a.kv_heads), gk = g * a.maps + mp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();
     const int pos = (pos_dev ? *pos_dev : p0) + t;
-    const float* q = Q + (size_t)t * a.heads * a.dim + (size_t)h * a.dim;
+    const float* q = Q + (size_t)t * a.heads * a.maps * a.dim + (size_t)hm * a.dim;
     for (int i = threadIdx.x; i < a.dim; i += AW_WARPS * 32) qs[i] = q[i];
     __syncthreads();
     if (splits > 1) cluster.sync();                          // every CTA of the cluster is resident before anyone writes into a peer's shared memory
     // visible keys: [0, n_first) and [lo, pos]
-    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    const int n_first = min(a.keep, lo);
+    const int lo = a.chunk > 0 ? (pos / a.chunk) * a.chunk : (a.window > 0 ? max(0, pos - a.window + 1) : 0);
+    const int n_first = a.chunk > 0 ? 0 : min(a.keep, lo);
     const int n_keys = n_first + (pos - lo + 1);
-    const size_t kstride = (size_t)a.kv_heads * a.dim, vstride = (size_t)a.kv_heads * a.vdim;
+    const size_t kstride = (size_t)a.kv_heads * a.maps * a.dim, vstride = (size_t)a.kv_heads * a.vdim;
     constexpr int PER16 = 16 / (int)sizeof(KT);
     const bool vec = a.dim % PER16 == 0 && (reinterpret_cast<uintptr_t>(kc) & 15) == 0;      // every key row then starts on 16 bytes
     float m = -FLT_MAX, l = 0.f, acc[AW_MAXV];
@@ -107,7 +108,7 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
         const int j = valid ? (n < n_first ? n : lo + (n - n_first)) : 0;
         float sc = -FLT_MAX;
         if (valid) {
-            sc = dot_row(kc + (size_t)j * kstride + (size_t)g * a.dim, qs, a.dim, vec) * a.scale;
+            sc = dot_row(kc + (size_t)j * kstride + (size_t)gk * a.dim, qs, a.dim, vec) * a.scale;
             if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
         }
         float gmax = sc;
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(float* 
     for (int w = 0; w < AW_WARPS; w++) M = fmaxf(M, ms[w]);
     float L = 0.f;
     for (int w = 0; w < AW_WARPS; w++) L += ls[w] * expf(ms[w] - M);
-    float* o = out + (size_t)t * a.heads * a.vdim + (size_t)h * a.vdim;
+    float* o = out + (size_t)t * a.heads * a.maps * a.vdim + (size_t)hm * a.vdim;
     if (splits == 1) {
         for (int i = threadIdx.x; i < a.vdim; i += AW_WARPS * 32) {
             float v = 0.f;
@@ -227,11 +228,12 @@ void attention_window(float* out, const float* Q, const void* kc, const void* vc
     if (tokens <= 0) return;
     // A single decoded token has only `heads` CTAs: split each head's keys over a thread-block cluster (one CTA per ~256 keys of
     // the longest visible range), merged through the leader's shared memory.  Prompt portions have CTAs enough without it.
-    const int longest = a.window > 0 ? std::min(max_seq, a.window + a.keep) : max_seq;
+    const int longest = a.chunk > 0 ? std::min(max_seq, a.chunk) : (a.window > 0 ? std::min(max_seq, a.window + a.keep) : max_seq);
     const int splits = tokens == 1 ? std::max(1, std::min(AW_MAX_SPLITS, (longest + 255) / 256)) : 1;
     const size_t smem = sizeof(float) * ((size_t)((a.dim + 3) & ~3) + (size_t)AW_WARPS * a.vdim + 2 * AW_WARPS + (size_t)splits * (a.vdim + 2));
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(tokens, a.heads, splits); cfg.blockDim = dim3(AW_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    NT_CHECK(a.maps >= 1, "attention_window: maps >= 1");
+    cfg.gridDim = dim3(tokens, a.heads * a.maps, splits); cfg.blockDim = dim3(AW_WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;
     cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;

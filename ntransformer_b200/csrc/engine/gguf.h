@@ -26,6 +26,8 @@ struct ModelConfig {                       // reference src/model/config.h:16-58
     // Families described layer by layer (a model folder, engine/model_registry.h): one entry per layer; empty for the GGUF Llama block.
     std::vector<LayerSpec> layers;
     float residual_mult = 1.0f;            // m of the PARALLEL block form
+    int streams = 0;                       // STREAMS block form: residual streams (0: a single residual, no stream tensors)
+    float embed_scale = 1.0f;              // the embedding row is multiplied by this
     bool layer_spec() const { return !layers.empty(); }
     void print() const;
 };

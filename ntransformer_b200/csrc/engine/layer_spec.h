@@ -12,7 +12,22 @@ enum class MixerKind { ATTN_ROPE_CAUSAL = 0,     // rotary positions, full causa
 enum class QKNorm { NONE = 0, WHOLE = 1 };       // WHOLE: one RMS norm across ALL heads of the projection (gain vector of that length)
 enum class GluAct { SILU = 0, GELU_TANH = 1 };
 enum class BlockForm { SEQUENTIAL = 0,           // x += mixer(norm1 x) ; x += ff(norm2 x)
-                       PARALLEL = 1 };           // h = norm1 x ; x += m * (ls1 * mixer(h) + ls2 * ff(h))
+                       PARALLEL = 1,             // h = norm1 x ; x += m * (ls1 * mixer(h) + ls2 * ff(h))
+                       STREAMS = 2 };            // SEQUENTIAL over several residual streams: a sublayer reads a learned blend of the streams and
+                                                 // its output enters every stream through a learned stream-mixing matrix (ModelConfig::streams)
+enum class FfKind { GLU = 0,                     // W_down (act(W_gate h) * W_up h)
+                    MOE_RELU2 = 1 };             // routed experts W_down relu(W_up h)^2, top-k softmax over the chosen logits, optional gated shared expert
+
+// Rotary positions of one attention layer.  dims == 0: none.  The first `dims` channels of a head rotate, the rest pass.
+// factor > 0 selects the long-context blend: channel pairs whose wavelength is long against `original` positions are slowed by
+// `factor`, short ones are left, with a linear ramp between the pair indices that turn `fast` and `slow` times over `original`;
+// cos and sin are then multiplied by 0.1 * ln(factor) + 1.
+struct RotarySpec {
+    int dims = 0;
+    float base = 10000.f;
+    bool interleaved = true;     // pairs (2i, 2i+1); false: (i, i + dims/2)
+    float factor = 0.f, original = 0.f, fast = 0.f, slow = 0.f;
+};
 
 struct LayerSpec {
     MixerKind mixer = MixerKind::ATTN_ROPE_CAUSAL;
@@ -29,6 +44,16 @@ struct LayerSpec {
     GluAct act = GluAct::SILU;
     bool layer_scale = false;    // per-channel gains on each branch before the residual sum
     int weights_of = -1;         // >= 0: this layer reads that layer's tensors (own KV cache)
+    // ---- mechanisms added with the Vebotar family; every one is off at its default ----
+    RotarySpec rot;              // rotary positions on q and k before the cache write
+    int chunk = 0;               // > 0: key j visible from i iff j <= i and j / chunk == i / chunk (blocks counted from position 0)
+    int maps = 1;                // 2: differential attention — two score maps per head ([map 1 | map 2] inside each q / k head) over one
+                                 // set of values, out = A1 v - lambda * A2 v, then a weightless RMS norm per head times (1 - diff)
+    float diff = 0.f;            // lambda = exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff
+    int kv_from = -1;            // >= 0: no key / value projections; reads that layer's cache rows (rotated keys, values)
+    FfKind ff_kind = FfKind::GLU;
+    int experts = 0, top = 0;    // MOE_RELU2: routed experts of width ff, experts used per token
+    int shared_ff = 0;           // MOE_RELU2: width of the shared expert (0 = none); its output is scaled by sigmoid(<w_sg, h>)
 };
 
 }}  // namespace nt::b200

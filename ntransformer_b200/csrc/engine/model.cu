@@ -74,9 +74,12 @@ Model::~Model() {
     for (void* p : {(void*)pf_.x, (void*)pf_.q, (void*)pf_.k, (void*)pf_.v, (void*)pf_.attn, pf_.ws, pf_.ws2, (void*)pf_.tok, (void*)pf_.pos,
                     (void*)pf_.g, (void*)pf_.u, pf_.whi, pf_.wlo})
         if (p) cudaFree(p);
-    for (void* p : kcs_) if (p) cudaFree(p);
-    for (void* p : vcs_) if (p) cudaFree(p);
-    for (void* p : {(void*)pf_.h, (void*)pf_.tmp, pf_.hws, (void*)want_out_}) if (p) cudaFree(p);
+    for (size_t i = 0; i < kcs_.size(); i++) if (kcs_[i] && (cache_owned_.empty() || cache_owned_[i])) { cudaFree(kcs_[i]); cudaFree(vcs_[i]); }
+    for (void* p : {(void*)pf_.h, (void*)pf_.tmp, pf_.hws, (void*)want_out_, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt,
+                    (void*)pf_.sgate, (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)streams_, (void*)sub_y_, (void*)maps_out_, (void*)moe_sel_,
+                    (void*)moe_wt_, (void*)moe_sgate_, (void*)moe_act_, (void*)ident_tab_})
+        if (p) cudaFree(p);
+    for (LayerWeights& L : layers_) for (void* p : {(void*)L.e_up_tab, (void*)L.e_down_tab, (void*)L.rot_freq}) if (p) cudaFree(p);
     if (argmax_host_) cudaFreeHost(argmax_host_);
     if (stream_) cudaStreamDestroy(stream_);
 }
@@ -111,7 +114,7 @@ void Model::init(const ModelConfig& cfg, int tp_rank, int tp_size) {
 bool Model::set_tensor(const std::string& name, const void* ptr, DType dt, size_t pitch) {
     if (cfg_.layer_spec()) {
         for (const TensorBinding& b : family_->tensors(cfg_))
-            if (b.name == name) return bind_slot(b.slot, b.layer, ptr, dt, b.rows, b.cols, pitch);
+            if (b.name == name) return bind_slot(b.slot, b.layer, ptr, dt, b.rows, b.cols, pitch, b.index);
         return false;
     }
     const int hidden = cfg_.hidden_size, hd = cfg_.head_dim;
@@ -403,7 +406,8 @@ void Model::clear_kv() {
         for (int i = 0; i < cfg_.n_layers; i++) {
             const LayerSpec& L = cfg_.layers[(size_t)i];
             const size_t es = dtype_size(cache_dt_);
-            NT_CUDA_CHECK(cudaMemsetAsync(kcs_[(size_t)i], 0, es * cfg_.max_seq_len * L.kv_heads * L.dim, stream_));
+            if (!cache_owned_[(size_t)i]) continue;
+            NT_CUDA_CHECK(cudaMemsetAsync(kcs_[(size_t)i], 0, es * cfg_.max_seq_len * L.kv_heads * L.maps * L.dim, stream_));
             NT_CUDA_CHECK(cudaMemsetAsync(vcs_[(size_t)i], 0, es * cfg_.max_seq_len * L.kv_heads * L.vdim, stream_));
         }
         return;
@@ -419,6 +423,10 @@ size_t Model::weight_bytes() const {
         for (int i = 0; i < cfg_.n_layers; i++) {
             const LayerWeights& L = layer_weights(i);
             b += L.wq.bytes() + L.wk.bytes() + L.wv.bytes() + L.wo.bytes() + L.gate.bytes() + L.up.bytes() + L.down.bytes();
+            // a decoded token reads the router, `top` of the experts and the shared expert
+            const LayerSpec& S = cfg_.layers[(size_t)i];
+            if (S.ff_kind == FfKind::MOE_RELU2 && S.ff > 0)
+                b += (size_t)S.experts * cfg_.hidden_size * 4 + (size_t)S.top * (L.e_up[0].bytes() + L.e_down[0].bytes()) + L.sh_up.bytes() + L.sh_down.bytes();
         }
         return b;
     }
@@ -429,7 +437,8 @@ size_t Model::weight_bytes() const {
 size_t Model::bytes_per_token(int ctx) const {
     if (cfg_.layer_spec()) {
         size_t b = weight_bytes();
-        for (const LayerSpec& L : cfg_.layers) b += (size_t)std::min(ctx, L.window + L.keep_first) * L.kv_heads * (L.dim + L.vdim) * dtype_size(cache_dt_);
+        for (const LayerSpec& L : cfg_.layers)
+            b += (size_t)std::min(ctx, L.chunk > 0 ? L.chunk : (L.window > 0 ? L.window + L.keep_first : ctx)) * L.kv_heads * (L.maps * L.dim + L.vdim) * dtype_size(cache_dt_);
         return b;
     }
     return weight_bytes() + (size_t)2 * cfg_.n_layers * ctx * nkv_l_ * cfg_.head_dim * 2;

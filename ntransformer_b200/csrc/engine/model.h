@@ -40,6 +40,19 @@ struct LayerWeights {
     const float* k_norm = nullptr;
     const float* ls1 = nullptr;
     const float* ls2 = nullptr;
+    // differential attention: the four vectors of lambda; residual streams, sublayer 0 (mixer) and 1 (feed-forward): read blend [S],
+    // write gains [S], stream mixing [S, S] (from, to); all F32, null when the mechanism is off
+    const float *lq1 = nullptr, *lk1 = nullptr, *lq2 = nullptr, *lk2 = nullptr;
+    const float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr};
+    // mixture of experts: router rows and the shared expert's gate row (F32), expert matrices, the shared expert
+    const float* router = nullptr;
+    const float* shared_gate = nullptr;
+    std::vector<Weight> e_up, e_down;
+    Weight sh_up, sh_down;
+    const void** e_up_tab = nullptr;       // device tables of the experts' row pointers (the chosen expert is looked up on the device)
+    const void** e_down_tab = nullptr;
+    float* rot_freq = nullptr;             // device, rot.dims / 2 angular frequencies (long-context blend applied), made at finalize
+    float rot_mag = 1.f;
 };
 
 class Model {
@@ -111,7 +124,12 @@ public:
 private:
     // ---- layer-spec families (engine/model_spec.cu) ----
     const LayerWeights& layer_weights(int i) const { const int j = cfg_.layer_spec() ? cfg_.layers[(size_t)i].weights_of : -1; return layers_[(size_t)(j >= 0 ? j : i)]; }
-    bool bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch);
+    bool bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch, int index = 0);
+    // STREAMS block form: one decoded token / a chunk of prompt rows
+    void layer_streams_token(int i, cudaStream_t s);
+    void layer_streams_rows(int i, int T, int p0, cudaStream_t s);
+    MoeWeights moe_of(int i, bool with_shared) const;
+    int n_streams() const { return cfg_.streams > 0 ? cfg_.streams : 1; }
     bool finalize_spec();
     void step_body_spec(cudaStream_t s);
     void step_head_spec(cudaStream_t s);
@@ -123,7 +141,14 @@ private:
     const ModelFamily* family_ = nullptr;
     bool exact32_ = false;
     DType cache_dt_ = DType::F16;
-    std::vector<void*> kcs_, vcs_;        // per-layer caches [max_seq, kv_heads * dim] / [max_seq, kv_heads * vdim] of cache_dt_
+    std::vector<void*> kcs_, vcs_;        // per-layer caches [max_seq, kv_heads * maps * dim] / [max_seq, kv_heads * vdim] of cache_dt_
+    std::vector<char> cache_owned_;       // 0: the layer reads another layer's cache rows (LayerSpec::kv_from)
+    float* streams_ = nullptr;            // decode: the residual streams [S, width]
+    float* sub_y_ = nullptr;              // decode: a sublayer's output before it enters the streams [width]
+    float* maps_out_ = nullptr;           // decode: the attention maps' outputs [heads * maps * vdim]
+    int* moe_sel_ = nullptr;              // decode: chosen experts [top], weights [top], shared gate [1], activations [top * ff + shared_ff]
+    float *moe_wt_ = nullptr, *moe_sgate_ = nullptr, *moe_act_ = nullptr;
+    float* ident_tab_ = nullptr;          // {1}: mixing matrix and write gain of a single residual stream
     std::vector<int> want_;               // places (indices into the current forward's tokens) whose logits are collected
     float* want_out_ = nullptr;           // device [want_cap_, vocab]
     size_t want_cap_ = 0;
@@ -182,6 +207,9 @@ private:
         int *tok = nullptr, *pos = nullptr;
         float *h = nullptr, *tmp = nullptr;   // layer-spec families: the block's normed input (read by both branches), a GEMM result before its scaled add
         void *hws = nullptr;                  // ... and its F16 hi/lo split
+        float *xs = nullptr, *maps = nullptr;     // STREAMS: the residual streams [T, S, width]; attention maps' outputs [T, heads * maps * vdim]
+        int *sel = nullptr, *work = nullptr;      // mixture of experts: chosen experts [T, top]; grouping tables
+        float *wt = nullptr, *sgate = nullptr, *act_rows = nullptr, *y_rows = nullptr;   // weights [T, top], shared gate [T], grouped rows [T*top, ff | width]
     } pf_;
     // Prompts shorter than this replay token by token through the decode chain (exact-integer GEMVs); longer ones take the batched
     // tensor-core prefill, whose F32 accumulation inside the tensor cores truncates once per 16-deep MMA step: ~1e-5..1e-4 per GEMM,

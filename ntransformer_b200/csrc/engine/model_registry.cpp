@@ -7,8 +7,17 @@
 namespace nt { namespace b200 {
 
 const std::vector<const ModelFamily*>& model_families() {
-    static const std::vector<const ModelFamily*> all = {zelunex_family()};
+    static const std::vector<const ModelFamily*> all = {zelunex_family(), vebotar_family()};
     return all;
+}
+
+bool slot_is_f32_table(TensorSlot s) {
+    switch (s) {
+        case TensorSlot::EMBED: case TensorSlot::HEAD: case TensorSlot::WQ: case TensorSlot::WK: case TensorSlot::WV: case TensorSlot::WO:
+        case TensorSlot::GATE: case TensorSlot::UP: case TensorSlot::DOWN: case TensorSlot::EXPERT_UP: case TensorSlot::EXPERT_DOWN:
+        case TensorSlot::SHARED_UP: case TensorSlot::SHARED_DOWN: return false;
+        default: return true;
+    }
 }
 
 const ModelFamily* find_model_family(const std::string& architecture) {

@@ -10,14 +10,20 @@
 
 namespace nt { namespace b200 {
 
-enum class TensorSlot { EMBED, HEAD, OUT_NORM, NORM1, NORM2, WQ, WK, WV, WO, Q_NORM, K_NORM, GATE, UP, DOWN, LS1, LS2 };
+enum class TensorSlot { EMBED, HEAD, OUT_NORM, NORM1, NORM2, WQ, WK, WV, WO, Q_NORM, K_NORM, GATE, UP, DOWN, LS1, LS2,
+                        LQ1, LK1, LQ2, LK2,                         // differential attention: the four vectors of lambda
+                        HC1_IN, HC1_OUT, HC1_MIX, HC2_IN, HC2_OUT, HC2_MIX,   // residual streams: read blend, write gains, stream mixing [from, to]
+                        ROUTER, EXPERT_UP, EXPERT_DOWN, SHARED_UP, SHARED_DOWN, SHARED_GATE };
 
 struct TensorBinding {
     std::string name;      // in the checkpoint
     TensorSlot slot;
     int layer;             // -1 for model-level tensors
     int rows, cols;        // expected shape (vectors: rows == 1)
+    int index = 0;         // which expert (EXPERT_UP / EXPERT_DOWN)
 };
+// Slots kept as F32 vectors / small F32 tables whatever the checkpoint stores (gains, lambda vectors, stream tables, router rows).
+bool slot_is_f32_table(TensorSlot s);
 
 struct ModelFamily {
     const char* architecture;
@@ -31,5 +37,6 @@ const std::vector<const ModelFamily*>& model_families();
 bool read_model_dir(const std::string& dir, ModelConfig& cfg, const ModelFamily** family);
 
 const ModelFamily* zelunex_family();      // engine/zelunex.cpp
+const ModelFamily* vebotar_family();      // engine/vebotar.cpp
 
 }}  // namespace nt::b200

@@ -15,6 +15,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <cmath>
 #include <cstring>
 #include <sys/stat.h>
 
@@ -40,7 +41,7 @@ bool Model::load(const std::string& path, int max_context) {
     return load_gguf(path, max_context);
 }
 
-bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch) {
+bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int rows, int cols, size_t pitch, int index) {
     auto W = [&](Weight& w) {
         if (!dense_dtype(dt)) return false;
         w.ptr = ptr; w.dtype = dt; w.rows = rows; w.cols = cols; w.pitch = pitch ? pitch : dtype_row_size(dt, (size_t)cols); w.owned = false;
@@ -66,6 +67,27 @@ bool Model::bind_slot(TensorSlot slot, int layer, const void* ptr, DType dt, int
         case TensorSlot::GATE: return W(L.gate);
         case TensorSlot::UP: return W(L.up);
         case TensorSlot::DOWN: return W(L.down);
+        case TensorSlot::LQ1: return V(L.lq1);
+        case TensorSlot::LK1: return V(L.lk1);
+        case TensorSlot::LQ2: return V(L.lq2);
+        case TensorSlot::LK2: return V(L.lk2);
+        case TensorSlot::HC1_IN: return V(L.hc_in[0]);
+        case TensorSlot::HC1_OUT: return V(L.hc_out[0]);
+        case TensorSlot::HC1_MIX: return V(L.hc_mix[0]);
+        case TensorSlot::HC2_IN: return V(L.hc_in[1]);
+        case TensorSlot::HC2_OUT: return V(L.hc_out[1]);
+        case TensorSlot::HC2_MIX: return V(L.hc_mix[1]);
+        case TensorSlot::ROUTER: return V(L.router);
+        case TensorSlot::SHARED_GATE: return V(L.shared_gate);
+        case TensorSlot::SHARED_UP: return W(L.sh_up);
+        case TensorSlot::SHARED_DOWN: return W(L.sh_down);
+        case TensorSlot::EXPERT_UP: case TensorSlot::EXPERT_DOWN: {
+            const int E = cfg_.layers[(size_t)layer].experts;
+            if (index < 0 || index >= E) return false;
+            std::vector<Weight>& v = slot == TensorSlot::EXPERT_UP ? L.e_up : L.e_down;
+            if ((int)v.size() != E) v.assign((size_t)E, Weight{});
+            return W(v[(size_t)index]);
+        }
         default: return false;
     }
 }
@@ -95,8 +117,7 @@ bool Model::load_dir(const std::string& dir, int max_context) {
             fprintf(stderr, "model: tensor %s does not have the shape the configuration needs [%d x %d]\n", b.name.c_str(), b.rows, b.cols);
             return false;
         }
-        const bool is_vec = b.slot == TensorSlot::OUT_NORM || b.slot == TensorSlot::NORM1 || b.slot == TensorSlot::NORM2 || b.slot == TensorSlot::Q_NORM ||
-                            b.slot == TensorSlot::K_NORM || b.slot == TensorSlot::LS1 || b.slot == TensorSlot::LS2;
+        const bool is_vec = slot_is_f32_table(b.slot);
         const DType dst = (is_vec || exact32_) ? DType::F32 : ti->dtype;
         jobs.push_back({ti, &b, arena, dst});
         arena += ((size_t)b.rows * b.cols * dtype_size(dst) + 255) & ~(size_t)255;
@@ -124,7 +145,7 @@ bool Model::load_dir(const std::string& dir, int max_context) {
             dense_to_f32(reinterpret_cast<float*>(base + j.off), dev_stage, j.ti->dtype, n, st);
         }
         NT_CUDA_CHECK(cudaStreamSynchronize(st));          // the staging buffers are reused by the next tensor
-        if (!bind_slot(j.b->slot, j.b->layer, base + j.off, j.dst, j.b->rows, j.b->cols, 0)) { fprintf(stderr, "model: cannot bind %s\n", j.b->name.c_str()); ok = false; break; }
+        if (!bind_slot(j.b->slot, j.b->layer, base + j.off, j.dst, j.b->rows, j.b->cols, 0, j.b->index)) { fprintf(stderr, "model: cannot bind %s\n", j.b->name.c_str()); ok = false; break; }
     }
     cudaFreeHost(host);
     cudaFree(dev_stage);
@@ -139,10 +160,58 @@ bool Model::load_dir(const std::string& dir, int max_context) {
 bool Model::finalize_spec() {
     const int hidden = cfg_.hidden_size, max_seq = cfg_.max_seq_len;
     if (!embd_.ptr || !out_norm_ || !head_.ptr) { fprintf(stderr, "model: embedding / final norm / head missing\n"); return false; }
-    int qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1;
+    int qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1, mapmax = 1, moe_act = 1, topmax = 1;
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerSpec& S = cfg_.layers[(size_t)i];
         const LayerWeights& L = layer_weights(i);
+        if (S.form == BlockForm::STREAMS) {
+            LayerWeights& M = layers_[(size_t)i];
+            const bool kv_ok = S.kv_from >= 0 || (L.wk.ptr && L.wv.ptr);
+            bool ok = L.attn_norm && L.wq.ptr && kv_ok && L.wo.ptr && (S.maps == 1 || (L.lq1 && L.lk1 && L.lq2 && L.lk2));
+            if (cfg_.streams > 0) ok = ok && L.hc_in[0] && L.hc_out[0] && L.hc_mix[0] && (S.ff == 0 || (L.hc_in[1] && L.hc_out[1] && L.hc_mix[1]));
+            if (S.ff > 0) {
+                ok = ok && S.ff_kind == FfKind::MOE_RELU2 && L.ffn_norm && L.router && (int)L.e_up.size() == S.experts && (int)L.e_down.size() == S.experts;
+                const DType edt = ok ? L.e_up[0].dtype : DType::F32;
+                for (int e = 0; ok && e < S.experts; e++) ok = L.e_up[(size_t)e].ptr && L.e_down[(size_t)e].ptr && L.e_up[(size_t)e].dtype == edt && L.e_down[(size_t)e].dtype == edt;
+                if (S.shared_ff > 0) ok = ok && L.sh_up.ptr && L.sh_down.ptr && L.shared_gate && L.sh_up.dtype == edt && L.sh_down.dtype == edt;
+            }
+            if (!ok) { fprintf(stderr, "model: layer %d is missing tensors\n", i); return false; }
+            if (S.mixer != MixerKind::ATTN_WINDOW || S.maps < 1 || S.maps > 2) { fprintf(stderr, "model: layer %d: this mixer has no layer-spec kernels yet\n", i); return false; }
+            if (S.vdim > 256) { fprintf(stderr, "model: layer %d: value heads wider than 256 are not covered\n", i); return false; }
+            if (S.ff > 0) {                                   // device tables of the experts' matrices
+                std::vector<const void*> up((size_t)S.experts), down((size_t)S.experts);
+                for (int e = 0; e < S.experts; e++) { up[(size_t)e] = L.e_up[(size_t)e].ptr; down[(size_t)e] = L.e_down[(size_t)e].ptr; }
+                M.e_up_tab = dmalloc<const void*>((size_t)S.experts);
+                M.e_down_tab = dmalloc<const void*>((size_t)S.experts);
+                NT_CUDA_CHECK(cudaMemcpy(M.e_up_tab, up.data(), sizeof(void*) * up.size(), cudaMemcpyHostToDevice));
+                NT_CUDA_CHECK(cudaMemcpy(M.e_down_tab, down.data(), sizeof(void*) * down.size(), cudaMemcpyHostToDevice));
+                moe_act = std::max(moe_act, S.top * S.ff + S.shared_ff);
+                topmax = std::max(topmax, S.top);
+            }
+            if (S.rot.dims > 0) {                             // angular frequencies in double, stored F32
+                const RotarySpec& R = S.rot;
+                const int half = R.dims / 2;
+                std::vector<float> f((size_t)half);
+                const double lnb = std::log((double)R.base);
+                auto turn = [&](double t) { return R.dims * std::log((double)R.original / (2.0 * M_PI * t)) / (2.0 * lnb); };
+                double lo = 0, hi = 0;
+                if (R.factor > 0.f) { lo = std::max(std::floor(turn(R.fast)), 0.0); hi = std::min(std::ceil(turn(R.slow)), (double)(R.dims - 1)); }
+                for (int k = 0; k < half; k++) {
+                    double fk = std::exp(-2.0 * k / R.dims * lnb);
+                    if (R.factor > 0.f) {
+                        const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
+                        fk = fk / R.factor * ramp + fk * (1.0 - ramp);
+                    }
+                    f[(size_t)k] = (float)fk;
+                }
+                M.rot_mag = R.factor > 0.f ? (float)(0.1 * std::log((double)R.factor) + 1.0) : 1.f;
+                M.rot_freq = dmalloc<float>((size_t)std::max(1, half));
+                NT_CUDA_CHECK(cudaMemcpy(M.rot_freq, f.data(), sizeof(float) * f.size(), cudaMemcpyHostToDevice));
+            }
+            qmax = std::max(qmax, S.heads * S.maps * S.dim); kmax = std::max(kmax, S.kv_heads * S.maps * S.dim); vmax = std::max(vmax, S.kv_heads * S.vdim);
+            omax = std::max(omax, S.heads * S.vdim); mapmax = std::max(mapmax, S.heads * S.maps * S.vdim);
+            continue;
+        }
         const bool mlp_ok = S.ff == 0 || (L.gate.ptr && L.up.ptr && L.down.ptr && (!S.layer_scale || L.ls2));
         if (!L.attn_norm || !L.wq.ptr || !L.wk.ptr || !L.wv.ptr || !L.wo.ptr || !mlp_ok || (S.layer_scale && !L.ls1) ||
             (S.qk_norm == QKNorm::WHOLE && (!L.q_norm || !L.k_norm))) {
@@ -160,14 +229,27 @@ bool Model::finalize_spec() {
     xnorm_ = dmalloc<float>(hidden);
     q_ = dmalloc<float>(qmax); k_ = dmalloc<float>(kmax); v_ = dmalloc<float>(vmax); attn_ = dmalloc<float>(omax);
     act_ = dmalloc<float>(ffmax);
+    if (cfg_.layers[0].form == BlockForm::STREAMS) {
+        const int S = n_streams();
+        streams_ = dmalloc<float>((size_t)S * hidden);
+        sub_y_ = dmalloc<float>(hidden);
+        part_ = dmalloc<float>(hidden);
+        maps_out_ = dmalloc<float>(mapmax);
+        moe_sel_ = dmalloc<int>(topmax); moe_wt_ = dmalloc<float>(topmax); moe_sgate_ = dmalloc<float>(1); moe_act_ = dmalloc<float>(moe_act);
+        ident_tab_ = dmalloc<float>(1);
+        const float one = 1.f;
+        NT_CUDA_CHECK(cudaMemcpy(ident_tab_, &one, sizeof(float), cudaMemcpyHostToDevice));
+    }
     logits_ = dmalloc<float>(cfg_.vocab_size);
     NT_CUDA_CHECK(cudaMemset(logits_, 0, sizeof(float) * (size_t)cfg_.vocab_size));
     kcs_.assign((size_t)cfg_.n_layers, nullptr);
     vcs_.assign((size_t)cfg_.n_layers, nullptr);
+    cache_owned_.assign((size_t)cfg_.n_layers, 1);
     const size_t es = dtype_size(cache_dt_);
-    for (int i = 0; i < cfg_.n_layers; i++) {          // every layer RUN owns a cache, also one that borrows its tensors
+    for (int i = 0; i < cfg_.n_layers; i++) {          // every layer RUN owns a cache, also one that borrows its tensors; not one that reads another's rows
         const LayerSpec& S = cfg_.layers[(size_t)i];
-        const size_t kb = es * max_seq * S.kv_heads * S.dim, vb = es * max_seq * S.kv_heads * S.vdim;
+        if (S.kv_from >= 0) { kcs_[(size_t)i] = kcs_[(size_t)S.kv_from]; vcs_[(size_t)i] = vcs_[(size_t)S.kv_from]; cache_owned_[(size_t)i] = 0; continue; }
+        const size_t kb = es * max_seq * S.kv_heads * S.maps * S.dim, vb = es * max_seq * S.kv_heads * S.vdim;
         if (cudaMalloc(&kcs_[(size_t)i], std::max<size_t>(kb, 16)) != cudaSuccess || cudaMalloc(&vcs_[(size_t)i], std::max<size_t>(vb, 16)) != cudaSuccess) {
             cudaGetLastError();
             fprintf(stderr, "model: cannot allocate the KV cache for %d tokens\n", max_seq);
@@ -187,6 +269,7 @@ bool Model::finalize_spec() {
 static WindowAttn attn_of(const LayerSpec& S) {
     WindowAttn a;
     a.heads = S.heads; a.kv_heads = S.kv_heads; a.dim = S.dim; a.vdim = S.vdim; a.window = S.window; a.keep = S.keep_first; a.scale = S.scale; a.softcap = S.softcap;
+    a.chunk = S.chunk; a.maps = S.maps;
     return a;
 }
 
@@ -195,6 +278,13 @@ void Model::step_body_spec(cudaStream_t s) {
     const int* pos_dev = step_dev_ + 1;
     const float m = cfg_.residual_mult;
     embed_rows(hidden_, embd_.ptr, embd_.dtype, step_dev_, 1, hidden, s);
+    if (cfg_.layers[0].form == BlockForm::STREAMS) {
+        // the residual lives in streams_ [S, width]; hidden_ holds the embedding row and, at the end, the sum of the streams for the head
+        streams_spread(streams_, hidden_, cfg_.embed_scale, 1, n_streams(), hidden, s);
+        for (int i = 0; i < cfg_.n_layers; i++) layer_streams_token(i, s);
+        streams_read(hidden_, streams_, nullptr, 1, n_streams(), hidden, s);
+        return;
+    }
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerSpec& S = cfg_.layers[(size_t)i];
         const LayerWeights& L = layer_weights(i);
@@ -227,13 +317,28 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     if (tokens <= pf_.cap) return;
     NT_CUDA_CHECK(cudaStreamSynchronize(stream_));
     for (void* p : {(void*)pf_.x, (void*)pf_.q, (void*)pf_.k, (void*)pf_.v, (void*)pf_.attn, (void*)pf_.g, (void*)pf_.u, (void*)pf_.h, (void*)pf_.tmp,
-                    pf_.ws, pf_.ws2, pf_.hws, (void*)pf_.tok})
+                    pf_.ws, pf_.ws2, pf_.hws, (void*)pf_.tok, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt, (void*)pf_.sgate,
+                    (void*)pf_.act_rows, (void*)pf_.y_rows})
         if (p) cudaFree(p);
+    pf_.xs = pf_.maps = pf_.wt = pf_.sgate = pf_.act_rows = pf_.y_rows = nullptr; pf_.sel = pf_.work = nullptr;
     const size_t T = (size_t)((tokens + 127) / 128 * 128), hidden = (size_t)cfg_.hidden_size;
-    size_t qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1;
+    size_t qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1, mapmax = 1, topmax = 0, emax = 1, effmax = 1;
     for (const LayerSpec& S : cfg_.layers) {
-        qmax = std::max(qmax, (size_t)S.heads * S.dim); kmax = std::max(kmax, (size_t)S.kv_heads * S.dim); vmax = std::max(vmax, (size_t)S.kv_heads * S.vdim);
-        omax = std::max(omax, (size_t)S.heads * S.vdim); ffmax = std::max(ffmax, (size_t)S.ff);
+        qmax = std::max(qmax, (size_t)S.heads * S.maps * S.dim); kmax = std::max(kmax, (size_t)S.kv_heads * S.maps * S.dim); vmax = std::max(vmax, (size_t)S.kv_heads * S.vdim);
+        omax = std::max(omax, (size_t)S.heads * S.vdim); mapmax = std::max(mapmax, (size_t)S.heads * S.maps * S.vdim);
+        if (S.ff_kind == FfKind::MOE_RELU2 && S.ff > 0) {
+            topmax = std::max(topmax, (size_t)S.top); emax = std::max(emax, (size_t)S.experts); effmax = std::max(effmax, (size_t)S.ff);
+            ffmax = std::max(ffmax, std::max((size_t)S.shared_ff, hidden));       // shared expert: activations [T, shared_ff], then its output [T, width]
+        } else ffmax = std::max(ffmax, (size_t)S.ff);
+    }
+    if (cfg_.layers[0].form == BlockForm::STREAMS) {
+        pf_.xs = dmalloc<float>(T * n_streams() * hidden);
+        pf_.maps = dmalloc<float>(T * mapmax);
+        if (topmax > 0) {
+            pf_.sel = dmalloc<int>(T * topmax); pf_.wt = dmalloc<float>(T * topmax); pf_.sgate = dmalloc<float>(T);
+            pf_.work = dmalloc<int>(moe_work_ints((int)T, (int)emax, (int)topmax));
+            pf_.act_rows = dmalloc<float>(T * topmax * effmax); pf_.y_rows = dmalloc<float>(T * topmax * hidden);
+        }
     }
     pf_.x = dmalloc<float>(T * hidden); pf_.h = dmalloc<float>(T * hidden); pf_.tmp = dmalloc<float>(T * hidden);
     pf_.q = dmalloc<float>(T * qmax); pf_.k = dmalloc<float>(T * kmax); pf_.v = dmalloc<float>(T * vmax); pf_.attn = dmalloc<float>(T * omax);
@@ -243,7 +348,7 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     bool any_tc = false;
     for (int i = 0; i < cfg_.n_layers; i++) {
         const LayerWeights& L = layer_weights(i);
-        for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down}) any_tc = any_tc || (w->ptr && spec_tc_ok(*w));
+        for (const Weight* w : {&L.wq, &L.wk, &L.wv, &L.wo, &L.gate, &L.up, &L.down, &L.sh_up, &L.sh_down}) any_tc = any_tc || (w->ptr && spec_tc_ok(*w));
     }
     if (any_tc) {                         // BF16 hi/lo splits of the three GEMM inputs (normed block input, attention output, gated activation)
         pf_.hws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)T, (int)hidden));
@@ -287,7 +392,10 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
         last_rows = T;
         NT_CUDA_CHECK(cudaMemcpyAsync(pf_.tok, tokens + c0, sizeof(int) * (size_t)T, cudaMemcpyHostToDevice, s));
         embed_rows(pf_.x, embd_.ptr, embd_.dtype, pf_.tok, T, hidden, s);
+        const bool streams_form = cfg_.layers[0].form == BlockForm::STREAMS;
+        if (streams_form) streams_spread(pf_.xs, pf_.x, cfg_.embed_scale, T, n_streams(), hidden, s);
         for (int i = 0; i < cfg_.n_layers; i++) {
+            if (streams_form) { layer_streams_rows(i, T, p0, s); continue; }
             const LayerSpec& S = cfg_.layers[(size_t)i];
             const LayerWeights& L = layer_weights(i);
             // the block's normed input feeds q, k, v, gate and up: as FP32 rows, as a BF16 split, or both, by what those matrices take
@@ -324,10 +432,110 @@ void Model::prefill_spec(const int* tokens, int seq_len, int start_pos) {
                 spec_gemm(pf_.x, pf_.g, down_tc ? pf_.ws2 : nullptr, L.down, T, DENSE_SCALED_ADD, L.ls2, m, s);
             }
         }
+        if (streams_form) streams_read(pf_.x, pf_.xs, nullptr, T, n_streams(), hidden, s);      // the sum of the streams feeds the head
         if (!want_.empty()) emit_wanted(pf_.x, c0, T, s);
     }
     copy(hidden_, pf_.x + (size_t)(last_rows - 1) * hidden, hidden, s);
     step_head(s);
+}
+
+// ---- BlockForm::STREAMS layers (differential attention, rotary positions, block-local mask, shared caches, mixture of experts) ----
+
+MoeWeights Model::moe_of(int i, bool with_shared) const {
+    const LayerSpec& S = cfg_.layers[(size_t)i];
+    const LayerWeights& L = layer_weights(i);
+    MoeWeights w;
+    w.router = L.router; w.shared_gate = S.shared_ff > 0 ? L.shared_gate : nullptr;
+    w.up = L.e_up_tab; w.down = L.e_down_tab; w.dtype = L.e_up[0].dtype;
+    w.experts = S.experts; w.top = S.top; w.ff = S.ff; w.width = cfg_.hidden_size;
+    if (with_shared && S.shared_ff > 0) { w.shared_up = L.sh_up.ptr; w.shared_down = L.sh_down.ptr; w.shared_ff = S.shared_ff; }
+    return w;
+}
+
+// One decoded token.  Launches: [read blend] [norm + q/k/v GEMV] [rotary + cache write] [attention, both maps] [differential combine]
+// [o GEMV] [stream write]   [read blend] [norm] [router] [experts up + relu^2] [experts down, weighted, + shared] [stream write]
+void Model::layer_streams_token(int i, cudaStream_t s) {
+    const LayerSpec& S = cfg_.layers[(size_t)i];
+    const LayerWeights& L = layer_weights(i);
+    const int hidden = cfg_.hidden_size, NS = n_streams();
+    const int* pos_dev = step_dev_ + 1;
+    const bool one = cfg_.streams == 0;            // a single residual: identity tables
+    const int qd = S.heads * S.maps * S.dim, kd = S.kv_heads * S.maps * S.dim, vd = S.kv_heads * S.vdim;
+    streams_read(xnorm_, streams_, one ? nullptr : L.hc_in[0], 1, NS, hidden, s);
+    if (S.kv_from < 0) {
+        GemvMat qkv[3] = {mat_of(L.wq, q_), mat_of(L.wk, k_), mat_of(L.wv, v_)};
+        gemv_dense(qkv, 3, hidden, xnorm_, DENSE_STORE, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps);
+    } else {
+        GemvMat q1 = mat_of(L.wq, q_);
+        gemv_dense(&q1, 1, hidden, xnorm_, DENSE_STORE, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps);
+    }
+    rope_partial_kv_write(q_, S.kv_from < 0 ? k_ : nullptr, v_, L.rot_freq, L.rot_mag, S.rot.dims, S.rot.interleaved, S.dim, kcs_[(size_t)i], vcs_[(size_t)i],
+                          cache_dt_, 1, pos_dev, 0, qd, kd, vd, s);
+    attention_window(S.maps > 1 ? maps_out_ : attn_, q_, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, 1, pos_dev, 0, cfg_.max_seq_len, attn_of(S), s);
+    if (S.maps > 1) diff_combine(attn_, maps_out_, L.lq1, L.lk1, L.lq2, L.lk2, S.dim, S.diff, cfg_.norm_eps, 1, S.heads, S.vdim, s);
+    GemvMat o = mat_of(L.wo, sub_y_);
+    gemv_dense(&o, 1, S.heads * S.vdim, attn_, DENSE_STORE, nullptr, 1.f, s);
+    streams_write(streams_, sub_y_, one ? ident_tab_ : L.hc_mix[0], one ? ident_tab_ : L.hc_out[0], 1, NS, hidden, s);
+    if (S.ff <= 0) return;
+    streams_read(xnorm_, streams_, one ? nullptr : L.hc_in[1], 1, NS, hidden, s);
+    rmsnorm(part_, xnorm_, L.ffn_norm, 1, hidden, cfg_.norm_eps, s);
+    const MoeWeights w = moe_of(i, true);
+    moe_route(moe_sel_, moe_wt_, moe_sgate_, part_, w, 1, s);
+    moe_expert_up_token(moe_act_, part_, moe_sel_, w, s);
+    moe_expert_down_token(sub_y_, moe_act_, moe_sel_, moe_wt_, moe_sgate_, nullptr, w, s);
+    streams_write(streams_, sub_y_, one ? ident_tab_ : L.hc_mix[1], one ? ident_tab_ : L.hc_out[1], 1, NS, hidden, s);
+}
+
+// T prompt rows at positions p0..: the same steps over rows; projections and the shared expert through spec_gemm (tensor cores
+// when the matrix qualifies), routed experts as gathered GEMMs over each expert's own rows.
+void Model::layer_streams_rows(int i, int T, int p0, cudaStream_t s) {
+    const LayerSpec& S = cfg_.layers[(size_t)i];
+    const LayerWeights& L = layer_weights(i);
+    const int hidden = cfg_.hidden_size, NS = n_streams();
+    const bool one = cfg_.streams == 0;
+    const int qd = S.heads * S.maps * S.dim, kd = S.kv_heads * S.maps * S.dim, vd = S.kv_heads * S.vdim;
+    streams_read(pf_.tmp, pf_.xs, one ? nullptr : L.hc_in[0], T, NS, hidden, s);
+    bool h_f32 = false, h_split = false;
+    auto reads_h = [&](const Weight& w) { if (spec_tc_ok(w)) h_split = true; else h_f32 = true; };
+    reads_h(L.wq);
+    if (S.kv_from < 0) { reads_h(L.wk); reads_h(L.wv); }
+    if (h_f32) rmsnorm(pf_.h, pf_.tmp, L.attn_norm, T, hidden, cfg_.norm_eps, s);
+    if (h_split) rmsnorm_split(pf_.hws, pf_.tmp, L.attn_norm, T, hidden, cfg_.norm_eps, s, true);
+    const float* hf = h_f32 ? pf_.h : nullptr;
+    const void* hs = h_split ? pf_.hws : nullptr;
+    spec_gemm(pf_.q, hf, hs, L.wq, T, DENSE_STORE, nullptr, 1.f, s);
+    if (S.kv_from < 0) {
+        spec_gemm(pf_.k, hf, hs, L.wk, T, DENSE_STORE, nullptr, 1.f, s);
+        spec_gemm(pf_.v, hf, hs, L.wv, T, DENSE_STORE, nullptr, 1.f, s);
+    }
+    rope_partial_kv_write(pf_.q, S.kv_from < 0 ? pf_.k : nullptr, pf_.v, L.rot_freq, L.rot_mag, S.rot.dims, S.rot.interleaved, S.dim, kcs_[(size_t)i],
+                          vcs_[(size_t)i], cache_dt_, T, nullptr, p0, qd, kd, vd, s);
+    attention_window(S.maps > 1 ? pf_.maps : pf_.attn, pf_.q, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, T, nullptr, p0, cfg_.max_seq_len, attn_of(S), s);
+    if (S.maps > 1) diff_combine(pf_.attn, pf_.maps, L.lq1, L.lk1, L.lq2, L.lk2, S.dim, S.diff, cfg_.norm_eps, T, S.heads, S.vdim, s);
+    const bool o_tc = spec_tc_ok(L.wo);
+    if (o_tc) split_activations(pf_.ws, pf_.attn, T, S.heads * S.vdim, s, true);
+    spec_gemm(pf_.tmp, pf_.attn, o_tc ? pf_.ws : nullptr, L.wo, T, DENSE_STORE, nullptr, 1.f, s);
+    streams_write(pf_.xs, pf_.tmp, one ? ident_tab_ : L.hc_mix[0], one ? ident_tab_ : L.hc_out[0], T, NS, hidden, s);
+    if (S.ff <= 0) return;
+    streams_read(pf_.tmp, pf_.xs, one ? nullptr : L.hc_in[1], T, NS, hidden, s);
+    rmsnorm(pf_.h, pf_.tmp, L.ffn_norm, T, hidden, cfg_.norm_eps, s);          // the router and the gathered expert GEMMs read F32 rows
+    const MoeWeights w = moe_of(i, false);
+    moe_route(pf_.sel, pf_.wt, pf_.sgate, pf_.h, w, T, s);
+    moe_group(pf_.work, pf_.sel, T, S.experts, S.top, s);
+    moe_expert_up_rows(pf_.act_rows, pf_.h, pf_.work, w, T, s);
+    moe_expert_down_rows(pf_.y_rows, pf_.act_rows, pf_.work, w, T, s);
+    const float* shared_y = nullptr;
+    if (S.shared_ff > 0) {
+        const bool up_tc = spec_tc_ok(L.sh_up), down_tc = spec_tc_ok(L.sh_down);
+        if (up_tc) rmsnorm_split(pf_.hws, pf_.tmp, L.ffn_norm, T, hidden, cfg_.norm_eps, s, true);
+        spec_gemm(pf_.g, pf_.h, up_tc ? pf_.hws : nullptr, L.sh_up, T, DENSE_STORE, nullptr, 1.f, s);
+        relu2(pf_.g, (size_t)T * S.shared_ff, s);
+        if (down_tc) split_activations(pf_.ws2, pf_.g, T, S.shared_ff, s, true);
+        spec_gemm(pf_.u, pf_.g, down_tc ? pf_.ws2 : nullptr, L.sh_down, T, DENSE_STORE, nullptr, 1.f, s);
+        shared_y = pf_.u;
+    }
+    moe_combine(pf_.tmp, pf_.y_rows, pf_.work, pf_.wt, pf_.sgate, shared_y, T, S.experts, S.top, hidden, s);
+    streams_write(pf_.xs, pf_.tmp, one ? ident_tab_ : L.hc_mix[1], one ? ident_tab_ : L.hc_out[1], T, NS, hidden, s);
 }
 
 }}  // namespace nt::b200

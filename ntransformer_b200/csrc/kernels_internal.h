@@ -145,6 +145,9 @@ struct WindowAttn {
     int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
     int window = 0, keep = 0;          // window == 0: full causal
     float scale = 1.f, softcap = 0.f;  // softcap == 0: none
+    int chunk = 0;                     // > 0 (instead of a window): key j visible from i iff j <= i and j / chunk == i / chunk
+    int maps = 1;                      // score maps per head: Q rows are [heads][maps][dim], key rows [kv_heads][maps][dim], values [kv_heads][vdim];
+                                       // every map is an attention of its own over the head's values; out [tokens, heads*maps*vdim]
 };
 // Q [tokens, heads*dim] at positions base.. (base = *pos_dev when pos_dev is given, else p0); caches [max_seq, kv_heads*dim|vdim] of
 // cache_dt (F32 or BF16) that already hold the rows of these tokens; out [tokens, heads*vdim].
@@ -158,6 +161,51 @@ void attention_window_mma(float* out, const float* Q, const void* kc, const void
 // Whole-projection RMS norm of the query rows (in place) and key rows (gains may be null: no norm), key/value rows -> cache rows base + t.
 void qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
                       DType cache_dt, int tokens, const int* pos_dev, int p0, int qdim, int kdim, int vdim, cudaStream_t s);
+
+// ---- rotary.cu / streams.cu / moe.cu: mechanisms of the layer-spec families beyond the first one ----
+// Rotary positions on the first `dims` channels of every `dim`-wide head of the query rows (in place) and key rows, then key / value
+// rows -> cache rows base + t.  freq: dims/2 angular frequencies (F32, device), mag multiplies cos and sin; pairs (2i, 2i+1) when
+// interleaved, else (i, i + dims/2).  K == nullptr: only the queries are rotated (a layer that reads another layer's cache).
+void rope_partial_kv_write(float* Q, const float* K, const float* V, const float* freq, float mag, int dims, bool interleaved, int dim,
+                           void* kc, void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0, int qdim, int kdim, int vdim, cudaStream_t s);
+// Differential combination of two attention maps: A [tokens, heads, 2, vdim] -> out [tokens, heads * vdim],
+// o = a1 - lambda * a2, out = o / sqrt(mean(o^2) + eps) * (1 - diff), lambda = exp(<lq1, lk1>) - exp(<lq2, lk2>) + diff (vectors of n_l).
+void diff_combine(float* out, const float* A, const float* lq1, const float* lk1, const float* lq2, const float* lk2, int n_l, float diff,
+                  float eps, int tokens, int heads, int vdim, cudaStream_t s);
+// Residual streams X [tokens, S, width].  spread: every stream <- scale * e.  read: u = sum_s a[s] X[s] (a == null: all ones).
+// write: X'[t] = sum_s M[s * S + t] X[s] + b[t] * y for all t at once.
+void streams_spread(float* X, const float* e, float scale, int tokens, int S, int width, cudaStream_t s);
+void streams_read(float* u, const float* X, const float* a, int tokens, int S, int width, cudaStream_t s);
+void streams_write(float* X, const float* y, const float* M, const float* b, int tokens, int S, int width, cudaStream_t s);
+void scale_rows(float* x, float scale, size_t n, cudaStream_t s);
+// Mixture of squared-ReLU experts.  h [tokens, width] F32 (already normed).
+struct MoeWeights {
+    const float* router = nullptr;       // [experts, width] F32
+    const float* shared_gate = nullptr;  // [width] F32 or null
+    const void* const* up = nullptr;     // device table [experts] of [ff, width] rows
+    const void* const* down = nullptr;   // device table [experts] of [width, ff] rows
+    const void* shared_up = nullptr;     // [shared_ff, width] / [width, shared_ff] of the same dtype, or null: the decode kernels
+    const void* shared_down = nullptr;   //   run the shared expert as one more slot
+    DType dtype = DType::BF16;           // of the expert matrices
+    int experts = 0, top = 0, ff = 0, width = 0, shared_ff = 0;
+};
+// Router: logits in F32, the `top` largest (lowest index on ties), softmax over the chosen -> sel [tokens, top], wt [tokens, top];
+// sgate [tokens] = sigmoid(<shared_gate, h>) when shared_gate is given.
+void moe_route(int* sel, float* wt, float* sgate, const float* h, const MoeWeights& w, int tokens, cudaStream_t s);
+// One token (decode): act [top * ff + shared_ff] = relu(W_up[sel] h)^2 ; y [width] = sum_k wt[k] * W_down[sel[k]] act[k] + sgate * shared part.
+void moe_expert_up_token(float* act, const float* h, const int* sel, const MoeWeights& w, cudaStream_t s);
+void moe_expert_down_token(float* y, const float* act, const int* sel, const float* wt, const float* sgate, const float* shared_y,
+                           const MoeWeights& w, cudaStream_t s);
+// Prompt rows: assignments grouped per expert (order inside an expert = token order), gathered GEMMs on CUDA cores in F32.
+//   work: ints [experts + 1 (offsets) + tokens*top (row -> token) + tokens*top (assignment -> row)]
+size_t moe_work_ints(int tokens, int experts, int top);
+void moe_group(int* work, const int* sel, int tokens, int experts, int top, cudaStream_t s);
+void moe_expert_up_rows(float* act_rows, const float* h, const int* work, const MoeWeights& w, int tokens, cudaStream_t s);     // [tokens*top, ff]
+void moe_expert_down_rows(float* y_rows, const float* act_rows, const int* work, const MoeWeights& w, int tokens, cudaStream_t s); // [tokens*top, width]
+// y [tokens, width] = sum_k wt[t, k] * y_rows[row(t, k)] (+ sgate[t] * shared_y[t])
+void moe_combine(float* y, const float* y_rows, const int* work, const float* wt, const float* sgate, const float* shared_y, int tokens,
+                 int experts, int top, int width, cudaStream_t s);
+void relu2(float* x, size_t n, cudaStream_t s);
 
 // Programmatic dependent launch (PDL): when enabled, kernels are launched with
 // cudaLaunchAttributeProgrammaticStreamSerialization so that a kernel's prologue (barrier init, TMA weight

@@ -756,6 +756,73 @@ FAMILY_SIZES = {
 }
 
 
+VEBOTAR_SIZES = {
+    # name: (width, heads, kv_heads, map dim, value dim, experts, top, expert ff, shared ff); the Zelunex model beside it has the same width and
+    # head counts, head dim = value dim, and a gated ff with as many weights as one token's experts use: (top * ff + shared) * 2 / 3
+    "2048_e8x2048": (2048, 16, 4, 64, 128, 8, 2, 2048, 2048),
+    "4096_e16x2048": (4096, 32, 8, 64, 128, 16, 4, 2048, 4096),
+}
+
+
+def run_family_compare_vebotar(args):
+    """--family-compare --family vebotar: prompt-pass and decode throughput of the Vebotar family (BF16 weights; differential attention
+    inside blocks of 1024 positions, 2 residual streams, routed experts) beside the closest existing family (Zelunex: BF16 weights,
+    window of 1024) at equal width, heads and active feed-forward weights.  Device-timed with CUDA events on the model's stream;
+    prompts differ between steps and the weights of either model exceed L2."""
+    import torch
+    from ntransformer_b200 import kernels as K
+    from ntransformer_b200.engine import Model
+    from ntransformer_b200.model_spec import vebotar_config, vebotar_random_tensors, zelunex_config, zelunex_random_tensors
+
+    torch.cuda.set_device(0)
+    n_layers, vocab, prompt_len, max_seq, span = 4, 32000, 2048, 4096, 1024
+    hbm, hbm_src = measured_peak_hbm()
+    rows = []
+    for name, (width, heads, kv, dim, vdim, experts, top, ff, sff) in VEBOTAR_SIZES.items():
+        vc = vebotar_config(vocab=vocab, width=width, n_layers=n_layers, heads=heads, kv_heads=kv, dim=dim, vdim=vdim, chunk=span, rot_dims=dim // 2,
+                            experts=experts, top=top, ff=ff, shared_ff=sff, streams=2, kv_from={n_layers - 1: n_layers - 2})
+        zc = zelunex_config(vocab=vocab, width=width, n_layers=n_layers, heads=heads, kv_heads=kv, dim=vdim, vdim=vdim, ff=(top * ff + sff) * 2 // 3 // 128 * 128,
+                            window=span)
+        row = {"size": name, "layers": n_layers, "prompt_tokens": prompt_len, "decode_context": prompt_len, "span": span}
+        for label, make in (("vebotar_bf16", lambda: Model.from_config_json(vc, vebotar_random_tensors(vc), max_context=max_seq)),
+                            ("zelunex_bf16", lambda: Model.from_config_json(zc, zelunex_random_tensors(zc), max_context=max_seq))):
+            model = make()
+            stream = torch.cuda.ExternalStream(model.stream)
+            prompts = [[token_at(i + 97 * j, vocab) for i in range(prompt_len)] for j in range(4)]
+            for i in range(args.warmup):
+                model.forward_async(prompts[i % 4], 0)
+            model.sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n0 = K.launch_count()
+            psteps = max(3, min(args.steps, 8))
+            a.record(stream)
+            for i in range(psteps):
+                model.forward_async(prompts[i % 4], 0)
+            b.record(stream)
+            model.sync()
+            prefill = psteps * prompt_len / (a.elapsed_time(b) / 1e3)
+            dsteps = max(8, min(args.steps, 256))
+            for i in range(args.warmup):
+                model.forward_async([token_at(i, vocab)], prompt_len + i)
+            model.sync()
+            a.record(stream)
+            for i in range(dsteps):
+                model.forward_async([token_at(i + 5, vocab)], prompt_len + args.warmup + i)
+            b.record(stream)
+            model.sync()
+            ms = a.elapsed_time(b) / dsteps
+            bpt = model.bytes_per_token(prompt_len + args.warmup + dsteps // 2)
+            row[label] = {"prefill_tok_s": round(prefill, 1), "decode_tok_s": round(1e3 / ms, 1), "decode_ms": round(ms, 4),
+                          "decode_bytes_per_token": bpt, "decode_frac_of_hbm_peak": round(bpt / (ms * 1e-3) / (hbm * 1e9), 3),
+                          "launches": int(K.launch_count() - n0)}
+            model.close()
+            del model
+            torch.cuda.empty_cache()
+        rows.append(row)
+    print(json.dumps({"metric": "family_compare", "family": "vebotar", "unit": "tok/s", "hbm_peak_gbs": hbm, "hbm_peak_source": hbm_src,
+                      "dtype": "bf16 weights, f32 activations", "data": "synthetic", "rows": rows}))
+
+
 def run_family_compare(args):
     """--family-compare: prompt-pass and decode throughput of the Zelunex family (BF16 weights, windowed attention) beside the
     closest GGUF family member (Llama block, F16 weights, full causal attention) at equal layer sizes.  Device-timed with CUDA
@@ -832,6 +899,8 @@ def main():
     ap.add_argument("--all-errs", action="store_true", help="--check only: list the error of every step, not the first 8")
     ap.add_argument("--family-compare", action="store_true",
                     help="instead of the workload: Zelunex beside the Llama block at equal layer sizes, prompt pass and decode (1 GPU)")
+    ap.add_argument("--family", default="zelunex", choices=["zelunex", "vebotar"],
+                    help="--family-compare only: zelunex beside the Llama block (default), or vebotar beside zelunex")
     ap.add_argument("--per-token-prompt", action="store_true", help="--check only: our engine replays the prompt token by token like the reference")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -841,7 +910,7 @@ def main():
         sys.exit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     if args.family_compare:
         if rank == 0:
-            run_family_compare(args)
+            (run_family_compare_vebotar if args.family == "vebotar" else run_family_compare)(args)
     elif args.check:
         run_check(args, rank, world)
     elif args.impl == "reference":

@@ -55,6 +55,26 @@ void nt_b200_attention_window(float* out, const float* Q, const void* kc, const 
 void nt_b200_qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
                               int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream);
 void nt_b200_glu_mul(float* out, const float* gate, const float* up, long long n, int gelu, void* stream);
+/* Attention with `maps` score maps per head (Q rows [heads][maps][dim], key rows [kv_heads][maps][dim], one value row per kv head) and a
+ * block-local causal mask (chunk > 0: j visible from i iff j <= i and j / chunk == i / chunk); out [tokens, heads * maps * vdim] */
+void nt_b200_attention_maps(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int heads, int kv_heads,
+                            int dim, int vdim, int chunk, int maps, float scale, int max_seq, void* stream);
+/* host: dims/2 angular frequencies (long-context blend when factor > 0); returns the multiplier of cos and sin */
+float nt_b200_rotary_table(float* freq_host, int dims, float base, float factor, float original, float fast, float slow);
+void nt_b200_rope_partial_kv_write(float* Q, const float* K, const float* V, const float* freq, float mag, int dims, int interleaved, int dim, void* kc,
+                                   void* vc, int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream);
+void nt_b200_diff_combine(float* out, const float* A, const float* lq1, const float* lk1, const float* lq2, const float* lk2, int n_l, float diff, float eps,
+                          int tokens, int heads, int vdim, void* stream);
+/* residual streams X [tokens, S, width] */
+void nt_b200_streams_spread(float* X, const float* e, float scale, int tokens, int S, int width, void* stream);
+void nt_b200_streams_read(float* u, const float* X, const float* a, int tokens, int S, int width, void* stream);
+void nt_b200_streams_write(float* X, const float* y, const float* M, const float* b, int tokens, int S, int width, void* stream);
+/* mixture of squared-ReLU experts: router (F32 rows) -> sel / wt [tokens, top], sgate [tokens]; experts through device pointer tables */
+void nt_b200_moe_route(int* sel, float* wt, float* sgate, const float* h, const float* router, const float* shared_gate, int experts, int top, int width,
+                       int tokens, void* stream);
+void nt_b200_moe_experts(float* y, const float* h, const int* sel, const float* wt, const float* sgate, const void* const* up_tab, const void* const* down_tab,
+                         const void* shared_up, const void* shared_down, const float* shared_y, int dtype, int experts, int top, int ff, int width,
+                         int shared_ff, int tokens, int mode, void* scratch, void* stream);
 
 /* forward(tokens[seq_len], start_pos): logits of the last token. logits_host may be NULL.  Returns 0. */
 int  nt_model_forward(nt_model_t m, const int* tokens_host, int seq_len, int start_pos, float* logits_host);

@@ -63,6 +63,15 @@ ENGINE_SIGNATURES = {
     "nt_b200_attention_window": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp]),
     "nt_b200_qk_norm_kv_write": (None, [_vp, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "nt_b200_glu_mul": (None, [_vp, _vp, _vp, C.c_longlong, _i, _vp]),
+    "nt_b200_attention_maps": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "nt_b200_rotary_table": (_f, [_vp, _i, _f, _f, _f, _f, _f]),
+    "nt_b200_rope_partial_kv_write": (None, [_vp, _vp, _vp, _vp, _f, _i, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "nt_b200_diff_combine": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _f, _f, _i, _i, _i, _vp]),
+    "nt_b200_streams_spread": (None, [_vp, _vp, _f, _i, _i, _i, _vp]),
+    "nt_b200_streams_read": (None, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "nt_b200_streams_write": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "nt_b200_moe_route": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "nt_b200_moe_experts": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "nt_tp_unique_id": (_i, [_vp]),
     "nt_tp_init": (_i, [_vp, _vp, _i, _i]),
 }

@@ -10,6 +10,8 @@
 #include "kernels_internal.h"
 #include "ring.cuh"
 #include <cuda_bf16.h>
+#include <algorithm>
+#include <cmath>
 
 namespace nt { namespace b200 {
 
@@ -142,6 +144,24 @@ __global__ void scale_rows_kernel(float* __restrict__ x, float scale, size_t n) 
 }
 
 }  // namespace
+
+float rotary_table(float* freq, int dims, float base, float factor, float original, float fast, float slow) {
+    const int half = dims / 2;
+    const double lnb = std::log((double)base), two_pi = 6.283185307179586476925;
+    // the (fractional) pair index whose wavelength fits `t` times into `original` positions
+    auto turn = [&](double t) { return dims * std::log((double)original / (two_pi * t)) / (2.0 * lnb); };
+    double lo = 0.0, hi = 0.0;
+    if (factor > 0.f) { lo = std::max(std::floor(turn(fast)), 0.0); hi = std::min(std::ceil(turn(slow)), (double)(dims - 1)); }
+    for (int i = 0; i < half; i++) {
+        double f = std::exp(-2.0 * i / dims * lnb);
+        if (factor > 0.f) {
+            const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
+            f = f / factor * ramp + f * (1.0 - ramp);
+        }
+        freq[i] = (float)f;
+    }
+    return factor > 0.f ? (float)(0.1 * std::log((double)factor) + 1.0) : 1.f;
+}
 
 void rope_partial_kv_write(float* Q, const float* K, const float* V, const float* freq, float mag, int dims, bool interleaved, int dim,
                            void* kc, void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0, int qdim, int kdim, int vdim, cudaStream_t s) {

@@ -53,17 +53,20 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <int HD, bool BF>
+// HD: query / key head width, HDV: value head width.  maps > 1: blockIdx.y walks (head, map) pairs — map m of head h scores against
+// map m of key head kvh (key rows [n_kv][maps][HD]) and sums kvh's one value row (value rows [n_kv][HDV]); n_heads counts the
+// (head, map) pairs.  chunk > 0 replaces the window rule: key j visible from p iff j <= p and j / chunk == p / chunk.
+template <int HD, int HDV, bool BF>
 __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__ out, const float* __restrict__ Q,
                                                              const __half* __restrict__ kc, const __half* __restrict__ vc,
                                                              int seq_len, int start_pos, int n_heads, int n_kv, int max_seq,
-                                                             float scale, int window, int keep, float softcap) {
-    constexpr int LD = HD + PAD, KS = HD / 16, NT = HD / 8;
+                                                             float scale, int window, int keep, float softcap, int maps, int chunk) {
+    constexpr int LD = HD + PAD, LDV = HDV + PAD, KS = HD / 16, NT = HDV / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* sK = reinterpret_cast<__half*>(smem_raw);                 // [2][BKV][LD]
-    __half* sV = sK + 2 * BKV * LD;                                   // [2][BKV][LD]
+    __half* sV = sK + 2 * BKV * LD;                                   // [2][BKV][LDV]
     const int qb = gridDim.x - 1 - blockIdx.x;                        // heaviest (latest) query blocks first
-    const int head = blockIdx.y, kvh = head / (n_heads / n_kv);
+    const int head = blockIdx.y, vh = (head / maps) / ((n_heads / maps) / n_kv), kvh = vh * maps + head % maps, n_k = n_kv * maps;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int r0 = qb * BQ + warp * 16 + g, r1 = r0 + 8;              // this thread's two query rows (chunk-relative)
     const int p0 = start_pos + r0, p1 = start_pos + r1;               // their absolute positions == last visible key
@@ -87,19 +90,23 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
 
     const int last_q = min(qb * BQ + BQ, seq_len) - 1;                // last valid query of the block
     // key tiles: those of the kept prefix that lie before the block's window, then the window's (full causal: all from tile 0)
-    const int first_win = window > 0 ? max(0, start_pos + qb * BQ - window + 1) / BKV : 0;
-    const int n_keep = window > 0 ? min((keep + BKV - 1) / BKV, first_win) : 0;
+    // (chunk: from the tile holding the first row of the first query's block of positions; later queries' blocks start no earlier)
+    const int first_win = chunk > 0 ? ((start_pos + qb * BQ) / chunk * chunk) / BKV : (window > 0 ? max(0, start_pos + qb * BQ - window + 1) / BKV : 0);
+    const int n_keep = (window > 0 && chunk <= 0) ? min((keep + BKV - 1) / BKV, first_win) : 0;
     const int n_tiles = n_keep + (start_pos + last_q) / BKV + 1 - first_win;
     auto tile_of = [&](int j) { return j < n_keep ? j : first_win + (j - n_keep); };
 
     auto load_tile = [&](int j, int st) {
-        constexpr int CH = HD / 8;                                    // 16-byte chunks per row
+        constexpr int CH = HD / 8, CHV = HDV / 8;                     // 16-byte chunks per row
         for (int c = threadIdx.x; c < BKV * CH; c += 128) {
             const int row = c / CH, ch = c % CH;
             const int key = min(tile_of(j) * BKV + row, max_seq - 1); // rows past the cache are masked by causality anyway
-            const size_t src = ((size_t)key * n_kv + kvh) * HD + ch * 8;
-            cp_async16(sK + ((size_t)st * BKV + row) * LD + ch * 8, kc + src);
-            cp_async16(sV + ((size_t)st * BKV + row) * LD + ch * 8, vc + src);
+            cp_async16(sK + ((size_t)st * BKV + row) * LD + ch * 8, kc + ((size_t)key * n_k + kvh) * HD + ch * 8);
+        }
+        for (int c = threadIdx.x; c < BKV * CHV; c += 128) {
+            const int row = c / CHV, ch = c % CHV;
+            const int key = min(tile_of(j) * BKV + row, max_seq - 1);
+            cp_async16(sV + ((size_t)st * BKV + row) * LDV + ch * 8, vc + ((size_t)key * n_kv + vh) * HDV + ch * 8);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -115,7 +122,7 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
         }
         __syncthreads();
         const __half* tK = sK + (size_t)st * BKV * LD;
-        const __half* tV = sV + (size_t)st * BKV * LD;
+        const __half* tV = sV + (size_t)st * BKV * LDV;
 
         // ---- S = Q K^T (16 x 64 per warp) ----
         float s[8][4];
@@ -140,7 +147,7 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
             for (int i = 0; i < 4; i++) {
                 const int key = key0 + n * 8 + 2 * t + (i & 1);
                 const int p = (i & 2) ? p1 : p0;
-                const bool seen = key <= p && (window <= 0 || p - key < window || key < keep);
+                const bool seen = key <= p && (chunk > 0 ? key >= p / chunk * chunk : (window <= 0 || p - key < window || key < keep));
                 float v = s[n][i] * scale;
                 if (softcap > 0.f) v = softcap * (1.0f - 2.0f / (__expf(2.0f * v / softcap) + 1.0f));     // cap * tanh(v / cap)
                 v = seen ? v : -INFINITY;
@@ -176,9 +183,9 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
             split2<BF>(s[2 * kt + 1][0], s[2 * kt + 1][1], phi[2], plo[2]);
             split2<BF>(s[2 * kt + 1][2], s[2 * kt + 1][3], phi[3], plo[3]);
 #pragma unroll
-            for (int np = 0; np < HD / 16; np++) {
+            for (int np = 0; np < HDV / 16; np++) {
                 // four 8x8 blocks of V^T: (keys +0..7 | +8..15) x (hd +0..7 | +8..15)
-                const __half* vp = tV + (size_t)(kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + np * 16 + (lane >> 4) * 8;
+                const __half* vp = tV + (size_t)(kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + np * 16 + (lane >> 4) * 8;
                 uint32_t v0, v1, v2, v3;
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                              : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"((uint32_t)__cvta_generic_to_shared(vp)));
@@ -196,19 +203,19 @@ __global__ void __launch_bounds__(128, 2) prefill_mma_kernel(float* __restrict__
 #pragma unroll
     for (int n = 0; n < NT; n++) {
         const int c = n * 8 + 2 * t;
-        if (r0 < seq_len) *reinterpret_cast<float2*>(out + ((size_t)r0 * n_heads + head) * HD + c) = make_float2(o[n][0] * i0, o[n][1] * i0);
-        if (r1 < seq_len) *reinterpret_cast<float2*>(out + ((size_t)r1 * n_heads + head) * HD + c) = make_float2(o[n][2] * i1, o[n][3] * i1);
+        if (r0 < seq_len) *reinterpret_cast<float2*>(out + ((size_t)r0 * n_heads + head) * HDV + c) = make_float2(o[n][0] * i0, o[n][1] * i0);
+        if (r1 < seq_len) *reinterpret_cast<float2*>(out + ((size_t)r1 * n_heads + head) * HDV + c) = make_float2(o[n][2] * i1, o[n][3] * i1);
     }
 }
 
-template <int HD, bool BF>
+template <int HD, int HDV, bool BF>
 void launch(float* out, const float* Q, const __half* kc, const __half* vc, int seq_len, int start_pos, int n_heads, int n_kv,
-            int max_seq, float scale, int window, int keep, float softcap, cudaStream_t s) {
-    const int smem = 2 * 2 * BKV * (HD + PAD) * (int)sizeof(__half);
+            int max_seq, float scale, int window, int keep, float softcap, cudaStream_t s, int maps = 1, int chunk = 0) {
+    const int smem = 2 * BKV * (HD + PAD + HDV + PAD) * (int)sizeof(__half);
     static unsigned long long configured = 0;      // bit per device id
-    opt_in_dynamic_smem(prefill_mma_kernel<HD, BF>, (int)(smem), configured);
-    prefill_mma_kernel<HD, BF><<<dim3((seq_len + BQ - 1) / BQ, n_heads), 128, smem, s>>>(out, Q, kc, vc, seq_len, start_pos, n_heads, n_kv,
-                                                                                        max_seq, scale, window, keep, softcap);
+    opt_in_dynamic_smem(prefill_mma_kernel<HD, HDV, BF>, (int)(smem), configured);
+    prefill_mma_kernel<HD, HDV, BF><<<dim3((seq_len + BQ - 1) / BQ, n_heads * maps), 128, smem, s>>>(out, Q, kc, vc, seq_len, start_pos, n_heads * maps, n_kv,
+                                                                                                    max_seq, scale, window, keep, softcap, maps, chunk);
     NT_LAUNCH_CHECK();
     count_launch();
 }
@@ -223,20 +230,26 @@ void attention_prefill_mma(float* out, const float* Q, const void* kc, const voi
                            int n_kv, int hd, int max_seq, float scale, cudaStream_t s) {
     const __half* k = static_cast<const __half*>(kc);
     const __half* v = static_cast<const __half*>(vc);
-    if (hd == 128) launch<128, false>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, 0, 0, 0.f, s);
-    else launch<64, false>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, 0, 0, 0.f, s);
+    if (hd == 128) launch<128, 128, false>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, 0, 0, 0.f, s);
+    else launch<64, 64, false>(out, Q, k, v, seq_len, start_pos, n_heads, n_kv, max_seq, scale, 0, 0, 0.f, s);
 }
 
-// Windowed / soft-capped form over a BF16 cache [max_seq][kv_heads][dim]: dim == vdim in {64, 128}, at least 16 queries.
+// Windowed / block-masked / soft-capped form over a BF16 cache: (dim, vdim) in {(64, 64), (128, 128), (32, 64), (64, 128)}, one or
+// two score maps per head, at least 16 queries.
 bool attention_window_mma_supported(int tokens, const WindowAttn& a, DType cache_dt) {
-    return cache_dt == DType::BF16 && a.dim == a.vdim && a.maps == 1 && a.chunk == 0 && attention_prefill_mma_supported(tokens, a.heads, a.kv_heads, a.dim);
+    const bool shape = (a.dim == a.vdim && (a.dim == 64 || a.dim == 128)) || (a.vdim == 2 * a.dim && (a.dim == 32 || a.dim == 64));
+    return cache_dt == DType::BF16 && shape && a.maps >= 1 && a.maps <= 2 && tokens >= 16 && a.kv_heads > 0 && a.heads % a.kv_heads == 0;
 }
 void attention_window_mma(float* out, const float* Q, const void* kc, const void* vc, int tokens, int p0, int max_seq, const WindowAttn& a,
                           cudaStream_t s) {
     const __half* k = static_cast<const __half*>(kc);       // 16-bit words either way; the BF instantiation reads them as BF16
     const __half* v = static_cast<const __half*>(vc);
-    if (a.dim == 128) launch<128, true>(out, Q, k, v, tokens, p0, a.heads, a.kv_heads, max_seq, a.scale, a.window, a.keep, a.softcap, s);
-    else launch<64, true>(out, Q, k, v, tokens, p0, a.heads, a.kv_heads, max_seq, a.scale, a.window, a.keep, a.softcap, s);
+#define NT_AW(D, V) launch<D, V, true>(out, Q, k, v, tokens, p0, a.heads, a.kv_heads, max_seq, a.scale, a.window, a.keep, a.softcap, s, a.maps, a.chunk)
+    if (a.dim == 128) NT_AW(128, 128);
+    else if (a.dim == 64 && a.vdim == 64) NT_AW(64, 64);
+    else if (a.dim == 64) NT_AW(64, 128);
+    else NT_AW(32, 64);
+#undef NT_AW
 }
 
 }}  // namespace nt::b200

@@ -96,7 +96,12 @@ int nt_model_dir_describe(const char* dir, char* out, size_t cap) {
         const LayerSpec& L = cfg.layers[i];
         text += "layer " + std::to_string(i) + ": heads=" + std::to_string(L.heads) + " kv=" + std::to_string(L.kv_heads) + " dim=" + std::to_string(L.dim) +
                 " vdim=" + std::to_string(L.vdim) + " window=" + std::to_string(L.window) + " keep=" + std::to_string(L.keep_first) + " ff=" + std::to_string(L.ff) +
-                " weights_of=" + std::to_string(L.weights_of) + "\n";
+                " weights_of=" + std::to_string(L.weights_of);
+        if (L.form == BlockForm::STREAMS)
+            text += " chunk=" + std::to_string(L.chunk) + " maps=" + std::to_string(L.maps) + " rot=" + std::to_string(L.rot.dims) + " kv_from=" + std::to_string(L.kv_from) +
+                    " experts=" + std::to_string(L.experts) + " top=" + std::to_string(L.top) + " shared_ff=" + std::to_string(L.shared_ff) +
+                    " streams=" + std::to_string(cfg.streams);
+        text += "\n";
     }
     size_t n = 0;
     for (const TensorBinding& b : fam->tensors(cfg)) {
@@ -150,6 +155,63 @@ void nt_b200_attention_window(float* out, const float* Q, const void* kc, const 
 void nt_b200_qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_gain, const float* k_gain, float eps, void* kc, void* vc,
                               int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream) {
     qk_norm_kv_write(Q, K, V, q_gain, k_gain, eps, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, qdim, kdim, vdim, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_attention_maps(float* out, const float* Q, const void* kc, const void* vc, int cache_dtype, int tokens, int p0, int heads, int kv_heads,
+                            int dim, int vdim, int chunk, int maps, float scale, int max_seq, void* stream) {
+    WindowAttn a;
+    a.heads = heads; a.kv_heads = kv_heads; a.dim = dim; a.vdim = vdim; a.chunk = chunk; a.maps = maps; a.scale = scale;
+    attention_window(out, Q, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, max_seq, a, static_cast<cudaStream_t>(stream));
+}
+float nt_b200_rotary_table(float* freq_host, int dims, float base, float factor, float original, float fast, float slow) {
+    return rotary_table(freq_host, dims, base, factor, original, fast, slow);
+}
+void nt_b200_rope_partial_kv_write(float* Q, const float* K, const float* V, const float* freq, float mag, int dims, int interleaved, int dim, void* kc,
+                                   void* vc, int cache_dtype, int tokens, int p0, int qdim, int kdim, int vdim, void* stream) {
+    rope_partial_kv_write(Q, K, V, freq, mag, dims, interleaved != 0, dim, kc, vc, (nt::DType)cache_dtype, tokens, nullptr, p0, qdim, kdim, vdim,
+                          static_cast<cudaStream_t>(stream));
+}
+void nt_b200_diff_combine(float* out, const float* A, const float* lq1, const float* lk1, const float* lq2, const float* lk2, int n_l, float diff, float eps,
+                          int tokens, int heads, int vdim, void* stream) {
+    diff_combine(out, A, lq1, lk1, lq2, lk2, n_l, diff, eps, tokens, heads, vdim, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_streams_spread(float* X, const float* e, float scale, int tokens, int S, int width, void* stream) {
+    streams_spread(X, e, scale, tokens, S, width, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_streams_read(float* u, const float* X, const float* a, int tokens, int S, int width, void* stream) {
+    streams_read(u, X, a, tokens, S, width, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_streams_write(float* X, const float* y, const float* M, const float* b, int tokens, int S, int width, void* stream) {
+    streams_write(X, y, M, b, tokens, S, width, static_cast<cudaStream_t>(stream));
+}
+void nt_b200_moe_route(int* sel, float* wt, float* sgate, const float* h, const float* router, const float* shared_gate, int experts, int top, int width,
+                       int tokens, void* stream) {
+    MoeWeights w;
+    w.router = router; w.shared_gate = shared_gate; w.experts = experts; w.top = top; w.width = width;
+    moe_route(sel, wt, sgate, h, w, tokens, static_cast<cudaStream_t>(stream));
+}
+// mode 0: the one-token kernels (tokens == 1; scratch: floats [top * ff + shared_ff]); mode 1: the grouped prompt-row kernels
+// (scratch: ints moe work table, then floats [tokens * top * (ff + width)]; the shared expert's output, if any, comes in shared_y)
+void nt_b200_moe_experts(float* y, const float* h, const int* sel, const float* wt, const float* sgate, const void* const* up_tab, const void* const* down_tab,
+                         const void* shared_up, const void* shared_down, const float* shared_y, int dtype, int experts, int top, int ff, int width,
+                         int shared_ff, int tokens, int mode, void* scratch, void* stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MoeWeights w;
+    w.up = up_tab; w.down = down_tab; w.dtype = (nt::DType)dtype; w.experts = experts; w.top = top; w.ff = ff; w.width = width;
+    if (mode == 0) {
+        w.shared_up = shared_up; w.shared_down = shared_down; w.shared_ff = shared_up ? shared_ff : 0;
+        float* act = static_cast<float*>(scratch);
+        moe_expert_up_token(act, h, sel, w, s);
+        moe_expert_down_token(y, act, sel, wt, sgate, nullptr, w, s);
+        return;
+    }
+    int* work = static_cast<int*>(scratch);
+    const size_t wi = (moe_work_ints(tokens, experts, top) + 3) & ~(size_t)3;
+    float* act_rows = reinterpret_cast<float*>(work + wi);
+    float* y_rows = act_rows + (size_t)tokens * top * ff;
+    moe_group(work, sel, tokens, experts, top, s);
+    moe_expert_up_rows(act_rows, h, work, w, tokens, s);
+    moe_expert_down_rows(y_rows, act_rows, work, w, tokens, s);
+    moe_combine(y, y_rows, work, wt, sgate, shared_y, tokens, experts, top, width, s);
 }
 void nt_b200_glu_mul(float* out, const float* gate, const float* up, long long n, int gelu, void* stream) {
     glu_mul(out, gate, up, (size_t)n, gelu != 0, static_cast<cudaStream_t>(stream));

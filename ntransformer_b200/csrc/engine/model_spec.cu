@@ -188,24 +188,11 @@ bool Model::finalize_spec() {
                 moe_act = std::max(moe_act, S.top * S.ff + S.shared_ff);
                 topmax = std::max(topmax, S.top);
             }
-            if (S.rot.dims > 0) {                             // angular frequencies in double, stored F32
+            if (S.rot.dims > 0) {
                 const RotarySpec& R = S.rot;
-                const int half = R.dims / 2;
-                std::vector<float> f((size_t)half);
-                const double lnb = std::log((double)R.base);
-                auto turn = [&](double t) { return R.dims * std::log((double)R.original / (2.0 * M_PI * t)) / (2.0 * lnb); };
-                double lo = 0, hi = 0;
-                if (R.factor > 0.f) { lo = std::max(std::floor(turn(R.fast)), 0.0); hi = std::min(std::ceil(turn(R.slow)), (double)(R.dims - 1)); }
-                for (int k = 0; k < half; k++) {
-                    double fk = std::exp(-2.0 * k / R.dims * lnb);
-                    if (R.factor > 0.f) {
-                        const double ramp = std::min(1.0, std::max(0.0, (k - lo) / std::max(hi - lo, 0.001)));
-                        fk = fk / R.factor * ramp + fk * (1.0 - ramp);
-                    }
-                    f[(size_t)k] = (float)fk;
-                }
-                M.rot_mag = R.factor > 0.f ? (float)(0.1 * std::log((double)R.factor) + 1.0) : 1.f;
-                M.rot_freq = dmalloc<float>((size_t)std::max(1, half));
+                std::vector<float> f((size_t)std::max(1, R.dims / 2));
+                M.rot_mag = rotary_table(f.data(), R.dims, R.base, R.factor, R.original, R.fast, R.slow);
+                M.rot_freq = dmalloc<float>(f.size());
                 NT_CUDA_CHECK(cudaMemcpy(M.rot_freq, f.data(), sizeof(float) * f.size(), cudaMemcpyHostToDevice));
             }
             qmax = std::max(qmax, S.heads * S.maps * S.dim); kmax = std::max(kmax, S.kv_heads * S.maps * S.dim); vmax = std::max(vmax, S.kv_heads * S.vdim);

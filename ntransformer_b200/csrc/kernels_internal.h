@@ -166,6 +166,9 @@ void qk_norm_kv_write(float* Q, const float* K, const float* V, const float* q_g
 // Rotary positions on the first `dims` channels of every `dim`-wide head of the query rows (in place) and key rows, then key / value
 // rows -> cache rows base + t.  freq: dims/2 angular frequencies (F32, device), mag multiplies cos and sin; pairs (2i, 2i+1) when
 // interleaved, else (i, i + dims/2).  K == nullptr: only the queries are rotated (a layer that reads another layer's cache).
+// Host: the dims/2 angular frequencies base^(-2i/dims) of a rotary layer, blended for long contexts when factor > 0 (see
+// engine/layer_spec.h RotarySpec), computed in double; returns the multiplier of cos and sin.
+float rotary_table(float* freq_host, int dims, float base, float factor, float original, float fast, float slow);
 void rope_partial_kv_write(float* Q, const float* K, const float* V, const float* freq, float mag, int dims, bool interleaved, int dim,
                            void* kc, void* vc, DType cache_dt, int tokens, const int* pos_dev, int p0, int qdim, int kdim, int vdim, cudaStream_t s);
 // Differential combination of two attention maps: A [tokens, heads, 2, vdim] -> out [tokens, heads * vdim],

@@ -140,3 +140,73 @@ def zelunex_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype=
             t[p + "mlp.down"] = mat(W, e["mlp"]["ff"])
             t[p + "ls2"] = vec(W)
     return t
+
+
+# ---- Vebotar (layer-spec family, model folders): synthetic configurations and random device weights for benchmarks ----
+def vebotar_config(vocab=32000, width=4096, n_layers=4, heads=32, kv_heads=8, dim=64, vdim=128, chunk=1024, rot_dims=32, rot_base=500000.0,
+                   scaling=(4.0, 8192, 32.0, 1.0), diff=0.3, experts=8, top=2, ff=4096, shared_ff=4096, streams=2, embed_scale=1.0, eps=1e-5,
+                   kv_from=None):
+    """The family's config.json as a dict.  dim is the width of ONE score map (a head has two).  kv_from: {layer: earlier layer whose
+    cache it reads}.  scaling: (factor, original, fast, slow) of the long-context frequency blend, or None."""
+    kv_from = kv_from or {}
+    layers = []
+    for i in range(n_layers):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "diff": diff, "mask": {"size": chunk},
+             "rot": {"dims": rot_dims, "base": rot_base}}
+        if scaling:
+            m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+        if i in kv_from:
+            m["kv_from"] = kv_from[i]
+        mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+        if shared_ff:
+            mlp["shared"] = {"ff": shared_ff}
+        layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    cfg = {"architecture": "Vebotar", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "layers": layers}
+    if streams:
+        cfg["streams"] = streams
+    return cfg
+
+
+def vebotar_random_tensors(config: dict, seed: int = 1234, device="cuda", dtype=None):
+    """Checkpoint name -> random CUDA tensor (matrices `dtype`, default bfloat16; gains, lambda vectors, stream tables, router float32)."""
+    import torch
+
+    dtype = dtype or torch.bfloat16
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    W, S = config["width"], config.get("streams", 0)
+
+    def mat(rows, cols, dt=dtype):
+        return (torch.randn(rows, cols, generator=g, device=device, dtype=torch.float32) * cols ** -0.5).to(dt)
+
+    def vec(n, mean=1.0, std=0.1):
+        return mean + std * torch.randn(n, generator=g, device=device, dtype=torch.float32)
+
+    t = {"embed": mat(config["vocab"], W) * W ** 0.5, "final.norm": vec(W), "head": mat(config["vocab"], W)}
+    for i, e in enumerate(config["layers"]):
+        m, p = e["mixer"], "l%d." % i
+        t[p + "norm1"] = vec(W)
+        t[p + "mix.q"] = mat(m["heads"] * 2 * m["dim"], W)
+        if "kv_from" not in m:
+            t[p + "mix.k"] = mat(m["kv_heads"] * 2 * m["dim"], W)
+            t[p + "mix.v"] = mat(m["kv_heads"] * m["vdim"], W)
+        for n in ("lq1", "lk1", "lq2", "lk2"):
+            t[p + "mix." + n] = vec(m["dim"], 0.0, 0.1)
+        t[p + "mix.o"] = mat(W, m["heads"] * m["vdim"])
+        subs = ["hc1."] + (["hc2."] if e.get("mlp") else [])
+        for q in subs if S else []:
+            t[p + q + "in"] = vec(S, 1.0 / S, 0.05)
+            t[p + q + "out"] = vec(S, 1.0, 0.05)
+            t[p + q + "mix"] = torch.eye(S, device=device) + 0.05 * torch.randn(S, S, generator=g, device=device)
+        if e.get("mlp"):
+            mlp = e["mlp"]
+            t[p + "norm2"] = vec(W)
+            t[p + "mlp.router"] = mat(mlp["router"]["experts"], W, torch.float32)
+            for x in range(mlp["router"]["experts"]):
+                t[p + "mlp.e%d.up" % x] = mat(mlp["expert"]["ff"], W)
+                t[p + "mlp.e%d.down" % x] = mat(W, mlp["expert"]["ff"])
+            if mlp.get("shared"):
+                t[p + "mlp.shared.up"] = mat(mlp["shared"]["ff"], W)
+                t[p + "mlp.shared.down"] = mat(W, mlp["shared"]["ff"])
+                t[p + "mlp.shared.sg"] = mat(1, W, torch.float32)
+    return t

@@ -178,3 +178,67 @@ def forward(cfg: dict, W: dict, tokens, layer_sums: list | None = None) -> np.nd
             layer_sums.append(X.sum(0))
     x = rms_norm(X.sum(0), W["final.norm"], eps)
     return x @ np.asarray(W["head"], dtype=np.float64).T
+
+
+# ---------------------------------------------------------------- random small models for the tests
+def _bf16(a):
+    """Round to the nearest bfloat16-representable value (ties to even), so a checkpoint written in bfloat16 holds the same numbers."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return u.astype(np.uint32).view(np.float32).astype(np.float64).reshape(np.shape(a))
+
+
+def random_model(rng, vocab=37, width=48, n_layers=3, heads=4, kv_heads=2, dim=8, vdim=12, chunk=7, rot_dims=4, base=50.0, scaling=True, diff=0.25,
+                 scale=None, experts=5, top=2, ff=20, shared_ff=14, streams=3, embed_scale=0.7, kv_from=None, no_mlp=(), eps=1e-5):
+    """(config dict, weights dict).  kv_from: {layer: earlier layer whose cache it reads}; streams 0: a single residual, no stream tensors."""
+    kv_from = kv_from or {}
+    layers = []
+    for i in range(n_layers):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale if scale is not None else dim ** -0.5), "diff": diff}
+        if chunk:
+            m["mask"] = {"size": chunk}
+        if rot_dims:
+            m["rot"] = {"dims": rot_dims, "base": base}
+            if scaling:
+                m["rot"]["scaling"] = {"factor": 3.0, "original": 24, "fast": 6.0, "slow": 1.5}
+        if i in kv_from:
+            m["kv_from"] = kv_from[i]
+        mlp = None
+        if i not in no_mlp:
+            mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+            if shared_ff:
+                mlp["shared"] = {"ff": shared_ff}
+        layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    cfg = {"architecture": "Vebotar", "vocab": vocab, "width": width, "norm": {"eps": eps}, "embedding": {"scale": embed_scale}, "layers": layers}
+    if streams:
+        cfg["streams"] = streams
+    mat = lambda r, c, s=1.0: _bf16(rng.standard_normal((r, c)) * s * c ** -0.5)
+    vec = lambda n: _bf16(1.0 + 0.2 * rng.standard_normal(n))
+    W = {"embed": _bf16(rng.standard_normal((vocab, width))), "final.norm": vec(width), "head": mat(vocab, width)}
+    for i, e in enumerate(layers):
+        p, m = "l%d." % i, e["mixer"]
+        W[p + "norm1"] = vec(width)
+        W[p + "mix.q"] = mat(heads * 2 * dim, width, 2.0)
+        if "kv_from" not in m:
+            W[p + "mix.k"] = mat(kv_heads * 2 * dim, width, 2.0)
+            W[p + "mix.v"] = mat(kv_heads * vdim, width)
+        for n in ("lq1", "lk1", "lq2", "lk2"):
+            W[p + "mix." + n] = _bf16(rng.standard_normal(dim) * 0.3)
+        W[p + "mix.o"] = mat(width, heads * vdim)
+        subs = ["hc1."] + (["hc2."] if e["mlp"] else [])
+        if streams:
+            for q in subs:
+                W[p + q + "in"] = _bf16(1.0 / streams + 0.3 * rng.standard_normal(streams))
+                W[p + q + "out"] = _bf16(1.0 + 0.3 * rng.standard_normal(streams))
+                W[p + q + "mix"] = _bf16(np.eye(streams) + 0.2 * rng.standard_normal((streams, streams)))
+        if e["mlp"]:
+            W[p + "norm2"] = vec(width)
+            W[p + "mlp.router"] = mat(experts, width, 2.0)
+            for x in range(experts):
+                W[p + "mlp.e%d.up" % x] = mat(ff, width)
+                W[p + "mlp.e%d.down" % x] = mat(width, ff)
+            if shared_ff:
+                W[p + "mlp.shared.up"] = mat(shared_ff, width)
+                W[p + "mlp.shared.down"] = mat(width, shared_ff)
+                W[p + "mlp.shared.sg"] = mat(1, width, 2.0)
+    return cfg, W

@@ -116,25 +116,45 @@ __global__ void streams_read_kernel(float* __restrict__ u, const float* __restri
     for (int s = 0; s < S; s++) { const float x = X[(t * S + s) * width + c]; acc = a ? fmaf(a[s], x, acc) : acc + x; }
     u[i] = acc;
 }
+// NS > 0: the number of streams is a compile-time constant (registers, S*S multiply-adds); NS == 0: any S <= MAX_STREAMS
+template <int NS>
 __global__ void streams_write_kernel(float* __restrict__ X, const float* __restrict__ y, const float* __restrict__ M, const float* __restrict__ b,
-                                     size_t n, int S, int width) {
+                                     size_t n, int S_rt, int width) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t t = i / width, c = i % width;
-    float x[MAX_STREAMS];
+    const float yv = y[i];
+    if (NS > 0) {
+        float x[NS > 0 ? NS : 1];
+#pragma unroll
+        for (int s = 0; s < NS; s++) x[s] = X[(t * NS + s) * width + c];
+#pragma unroll
+        for (int to = 0; to < NS; to++) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < NS; s++) acc = fmaf(M[s * NS + to], x[s], acc);
+            X[(t * NS + to) * width + c] = fmaf(b[to], yv, acc);
+        }
+        return;
+    }
+    const int S = S_rt;
+    float x[MAX_STREAMS], r[MAX_STREAMS];
 #pragma unroll
     for (int s = 0; s < MAX_STREAMS; s++) x[s] = s < S ? X[(t * S + s) * width + c] : 0.f;
-    const float yv = y[i];
 #pragma unroll
     for (int to = 0; to < MAX_STREAMS; to++) {
-        if (to >= S) break;
         float acc = 0.f;
+        if (to < S) {
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; s++) if (s < S) acc = fmaf(M[s * S + to], x[s], acc);
-        X[(t * S + to) * width + c] = fmaf(b[to], yv, acc);
+            for (int s = 0; s < MAX_STREAMS; s++) if (s < S) acc = fmaf(M[s * S + to], x[s], acc);
+            acc = fmaf(b[to], yv, acc);
+        }
+        r[to] = acc;
     }
+#pragma unroll
+    for (int to = 0; to < MAX_STREAMS; to++) if (to < S) X[(t * S + to) * width + c] = r[to];
 }
 __global__ void scale_rows_kernel(float* __restrict__ x, float scale, size_t n) {
     pdl_launch_dependents();
@@ -202,7 +222,12 @@ void streams_write(float* X, const float* y, const float* M, const float* b, int
     NT_CHECK(S >= 1 && S <= MAX_STREAMS, "streams_write: 1..16 streams");
     const size_t n = (size_t)tokens * width;
     if (!n) return;
-    launch_k(streams_write_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, X, y, M, b, n, S, width);
+    const dim3 grid((unsigned)((n + 255) / 256));
+    if (S == 1) launch_k(streams_write_kernel<1>, grid, dim3(256), 0, s, X, y, M, b, n, S, width);
+    else if (S == 2) launch_k(streams_write_kernel<2>, grid, dim3(256), 0, s, X, y, M, b, n, S, width);
+    else if (S == 3) launch_k(streams_write_kernel<3>, grid, dim3(256), 0, s, X, y, M, b, n, S, width);
+    else if (S == 4) launch_k(streams_write_kernel<4>, grid, dim3(256), 0, s, X, y, M, b, n, S, width);
+    else launch_k(streams_write_kernel<0>, grid, dim3(256), 0, s, X, y, M, b, n, S, width);
     count_launch();
 }
 void scale_rows(float* x, float scale, size_t n, cudaStream_t s) {

@@ -77,8 +77,9 @@ Model::~Model() {
     for (size_t i = 0; i < kcs_.size(); i++) if (kcs_[i] && (cache_owned_.empty() || cache_owned_[i])) { cudaFree(kcs_[i]); cudaFree(vcs_[i]); }
     for (void* p : {(void*)pf_.h, (void*)pf_.tmp, pf_.hws, (void*)want_out_, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt,
                     (void*)pf_.sgate, (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)streams_, (void*)sub_y_, (void*)maps_out_, (void*)moe_sel_,
-                    (void*)moe_wt_, (void*)moe_sgate_, (void*)moe_act_, (void*)ident_tab_})
+                    (void*)moe_wt_, (void*)moe_sgate_, (void*)moe_act_, (void*)ident_tab_, (void*)pf_.g2, pf_.moe_ws})
         if (p) cudaFree(p);
+    if (moe_offsets_host_) cudaFreeHost(moe_offsets_host_);
     for (LayerWeights& L : layers_) for (void* p : {(void*)L.e_up_tab, (void*)L.e_down_tab, (void*)L.rot_freq}) if (p) cudaFree(p);
     if (argmax_host_) cudaFreeHost(argmax_host_);
     if (stream_) cudaStreamDestroy(stream_);

@@ -148,6 +148,7 @@ private:
     float* maps_out_ = nullptr;           // decode: the attention maps' outputs [heads * maps * vdim]
     int* moe_sel_ = nullptr;              // decode: chosen experts [top], weights [top], shared gate [1], activations [top * ff + shared_ff]
     float *moe_wt_ = nullptr, *moe_sgate_ = nullptr, *moe_act_ = nullptr;
+    int* moe_offsets_host_ = nullptr;     // pinned: per-expert row offsets of the current prompt chunk (tensor-core expert GEMMs)
     float* ident_tab_ = nullptr;          // {1}: mixing matrix and write gain of a single residual stream
     std::vector<int> want_;               // places (indices into the current forward's tokens) whose logits are collected
     float* want_out_ = nullptr;           // device [want_cap_, vocab]
@@ -209,6 +210,7 @@ private:
         void *hws = nullptr;                  // ... and its F16 hi/lo split
         float *xs = nullptr, *maps = nullptr;     // STREAMS: the residual streams [T, S, width]; attention maps' outputs [T, heads * maps * vdim]
         int *sel = nullptr, *work = nullptr;      // mixture of experts: chosen experts [T, top]; grouping tables
+        float *g2 = nullptr; void *moe_ws = nullptr;   // tensor-core experts: rows gathered in expert order [T*top, width]; per-expert padded split workspace
         float *wt = nullptr, *sgate = nullptr, *act_rows = nullptr, *y_rows = nullptr;   // weights [T, top], shared gate [T], grouped rows [T*top, ff | width]
     } pf_;
     // Prompts shorter than this replay token by token through the decode chain (exact-integer GEMVs); longer ones take the batched

@@ -305,9 +305,9 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream_));
     for (void* p : {(void*)pf_.x, (void*)pf_.q, (void*)pf_.k, (void*)pf_.v, (void*)pf_.attn, (void*)pf_.g, (void*)pf_.u, (void*)pf_.h, (void*)pf_.tmp,
                     pf_.ws, pf_.ws2, pf_.hws, (void*)pf_.tok, (void*)pf_.xs, (void*)pf_.maps, (void*)pf_.sel, (void*)pf_.work, (void*)pf_.wt, (void*)pf_.sgate,
-                    (void*)pf_.act_rows, (void*)pf_.y_rows})
+                    (void*)pf_.act_rows, (void*)pf_.y_rows, (void*)pf_.g2, pf_.moe_ws})
         if (p) cudaFree(p);
-    pf_.xs = pf_.maps = pf_.wt = pf_.sgate = pf_.act_rows = pf_.y_rows = nullptr; pf_.sel = pf_.work = nullptr;
+    pf_.xs = pf_.maps = pf_.wt = pf_.sgate = pf_.act_rows = pf_.y_rows = pf_.g2 = nullptr; pf_.sel = pf_.work = nullptr; pf_.moe_ws = nullptr;
     const size_t T = (size_t)((tokens + 127) / 128 * 128), hidden = (size_t)cfg_.hidden_size;
     size_t qmax = 1, kmax = 1, vmax = 1, omax = 1, ffmax = 1, mapmax = 1, topmax = 0, emax = 1, effmax = 1;
     for (const LayerSpec& S : cfg_.layers) {
@@ -325,6 +325,11 @@ void Model::ensure_prefill_buffers_spec(int tokens) {
             pf_.sel = dmalloc<int>(T * topmax); pf_.wt = dmalloc<float>(T * topmax); pf_.sgate = dmalloc<float>(T);
             pf_.work = dmalloc<int>(moe_work_ints((int)T, (int)emax, (int)topmax));
             pf_.act_rows = dmalloc<float>(T * topmax * effmax); pf_.y_rows = dmalloc<float>(T * topmax * hidden);
+            if (!exact32_) {       // the tensor-core path of the routed experts: gathered rows, and a split workspace with every expert's rows padded to a tile
+                pf_.g2 = dmalloc<float>(T * topmax * hidden);
+                pf_.moe_ws = dmalloc<uint8_t>(gemm_f16_tc_workspace_bytes((int)(T * topmax + emax * 128), (int)std::max(hidden, effmax)));
+                if (!moe_offsets_host_) NT_CUDA_CHECK(cudaMallocHost(&moe_offsets_host_, sizeof(int) * 257));
+            }
         }
     }
     pf_.x = dmalloc<float>(T * hidden); pf_.h = dmalloc<float>(T * hidden); pf_.tmp = dmalloc<float>(T * hidden);
@@ -509,8 +514,40 @@ void Model::layer_streams_rows(int i, int T, int p0, cudaStream_t s) {
     const MoeWeights w = moe_of(i, false);
     moe_route(pf_.sel, pf_.wt, pf_.sgate, pf_.h, w, T, s);
     moe_group(pf_.work, pf_.sel, T, S.experts, S.top, s);
-    moe_expert_up_rows(pf_.act_rows, pf_.h, pf_.work, w, T, s);
-    moe_expert_down_rows(pf_.y_rows, pf_.act_rows, pf_.work, w, T, s);
+    bool experts_tc = pf_.moe_ws != nullptr;
+    for (int e = 0; experts_tc && e < S.experts; e++) experts_tc = spec_tc_ok(L.e_up[(size_t)e]) && spec_tc_ok(L.e_down[(size_t)e]);
+    if (experts_tc) {
+        // Tensor cores: the per-expert row counts come to the host (one small copy and a wait per layer), then every expert with rows
+        // runs the tcgen05 GEMM over exactly its rows: gather the rows in expert order, split per expert into its own padded
+        // region of the workspace, up GEMM, relu^2 over all rows at once, split again, down GEMM.
+        NT_CUDA_CHECK(cudaMemcpyAsync(moe_offsets_host_, pf_.work, sizeof(int) * (size_t)(S.experts + 1), cudaMemcpyDeviceToHost, s));
+        NT_CUDA_CHECK(cudaStreamSynchronize(s));
+        moe_gather_rows(pf_.g2, pf_.h, pf_.work, T, S.experts, S.top, hidden, s);
+        auto region = [&](size_t rows_before, int K) { return static_cast<uint8_t*>(pf_.moe_ws) + gemm_f16_tc_workspace_bytes((int)rows_before, K); };
+        TcOpts o; o.bf16 = true;
+        size_t padded = 0;
+        for (int e = 0; e < S.experts; e++) {
+            const int r0 = moe_offsets_host_[e], cnt = moe_offsets_host_[e + 1] - r0;
+            if (cnt <= 0) continue;
+            void* ws = region(padded, hidden);
+            split_activations(ws, pf_.g2 + (size_t)r0 * hidden, cnt, hidden, s, true);
+            NT_CHECK(gemm_f16_tc_ws(pf_.act_rows + (size_t)r0 * S.ff, ws, L.e_up[(size_t)e].ptr, cnt, S.ff, hidden, false, s, o), "expert GEMM (up) rejected");
+            padded += ((size_t)cnt + 127) / 128 * 128;
+        }
+        relu2(pf_.act_rows, (size_t)T * S.top * S.ff, s);
+        padded = 0;
+        for (int e = 0; e < S.experts; e++) {
+            const int r0 = moe_offsets_host_[e], cnt = moe_offsets_host_[e + 1] - r0;
+            if (cnt <= 0) continue;
+            void* ws = region(padded, S.ff);
+            split_activations(ws, pf_.act_rows + (size_t)r0 * S.ff, cnt, S.ff, s, true);
+            NT_CHECK(gemm_f16_tc_ws(pf_.y_rows + (size_t)r0 * hidden, ws, L.e_down[(size_t)e].ptr, cnt, hidden, S.ff, false, s, o), "expert GEMM (down) rejected");
+            padded += ((size_t)cnt + 127) / 128 * 128;
+        }
+    } else {
+        moe_expert_up_rows(pf_.act_rows, pf_.h, pf_.work, w, T, s);
+        moe_expert_down_rows(pf_.y_rows, pf_.act_rows, pf_.work, w, T, s);
+    }
     const float* shared_y = nullptr;
     if (S.shared_ff > 0) {
         const bool up_tc = spec_tc_ok(L.sh_up), down_tc = spec_tc_ok(L.sh_down);

@@ -208,6 +208,8 @@ void moe_expert_down_rows(float* y_rows, const float* act_rows, const int* work,
 // y [tokens, width] = sum_k wt[t, k] * y_rows[row(t, k)] (+ sgate[t] * shared_y[t])
 void moe_combine(float* y, const float* y_rows, const int* work, const float* wt, const float* sgate, const float* shared_y, int tokens,
                  int experts, int top, int width, cudaStream_t s);
+// h rows in the grouped order (the tensor-core path splits them per expert): out [tokens*top, width]
+void moe_gather_rows(float* out, const float* h, const int* work, int tokens, int experts, int top, int width, cudaStream_t s);
 void relu2(float* x, size_t n, cudaStream_t s);
 
 // Programmatic dependent launch (PDL): when enabled, kernels are launched with

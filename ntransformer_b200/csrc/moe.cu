@@ -44,6 +44,12 @@ template <> struct El<__nv_bfloat16> {
     }
 };
 
+__device__ __forceinline__ uint4 ld_nc16(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 // <row, xs> over K by one warp; vec: the row starts on 16 bytes and K is a multiple of the elements per 16 bytes
 template <typename T>
 __device__ __forceinline__ float warp_dot(const unsigned char* row, const float* xs, int K, int lane, bool vec) {
@@ -51,10 +57,23 @@ __device__ __forceinline__ float warp_dot(const unsigned char* row, const float*
     constexpr int P = El<T>::P;
     if (vec) {
         const int nv = K / P;
-#pragma unroll 4
-        for (int v = lane; v < nv; v += 32) {
+        int v = lane;
+        for (; v + 96 < nv; v += 128) {          // four 16-byte loads in flight per lane
+            uint4 w[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) w[u] = ld_nc16(reinterpret_cast<const uint4*>(row) + v + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float f[P];
+                El<T>::unpack(w[u], f);
+                const float* xp = xs + (size_t)(v + 32 * u) * P;
+#pragma unroll
+                for (int k = 0; k < P; k++) acc = fmaf(f[k], xp[k], acc);
+            }
+        }
+        for (; v < nv; v += 32) {
             float f[P];
-            El<T>::unpack(__ldg(reinterpret_cast<const uint4*>(row) + v), f);
+            El<T>::unpack(ld_nc16(reinterpret_cast<const uint4*>(row) + v), f);
             const float* xp = xs + (size_t)v * P;
 #pragma unroll
             for (int k = 0; k < P; k++) acc = fmaf(f[k], xp[k], acc);
@@ -253,6 +272,15 @@ __global__ void __launch_bounds__(256) moe_rows_gemm_kernel(float* __restrict__ 
     }
 }
 
+// rows in expert order: out[row] = h[row_token[row]]
+__global__ void moe_gather_rows_kernel(float* __restrict__ out, const float* __restrict__ h, const int* __restrict__ row_token, size_t n, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t r = i / width, c = i % width;
+    out[i] = h[(size_t)row_token[r] * width + c];
+}
 __global__ void moe_combine_kernel(float* __restrict__ y, const float* __restrict__ y_rows, const int* __restrict__ assign_row, const float* __restrict__ wt,
                                    const float* __restrict__ sgate, const float* __restrict__ shared_y, size_t n, int top, int width) {
     pdl_launch_dependents();
@@ -348,6 +376,12 @@ void moe_combine(float* y, const float* y_rows, const int* work, const float* wt
     if (!n) return;
     launch_k(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, y, y_rows, work + experts + 1 + (size_t)tokens * top, wt, sgate,
              shared_y, n, top, width);
+    count_launch();
+}
+void moe_gather_rows(float* out, const float* h, const int* work, int tokens, int experts, int top, int width, cudaStream_t s) {
+    const size_t n = (size_t)tokens * top * width;
+    if (!n) return;
+    launch_k(moe_gather_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, out, h, work + experts + 1, n, width);
     count_launch();
 }
 void relu2(float* x, size_t n, cudaStream_t s) {

@@ -244,8 +244,10 @@ CONFIGS = {
     "plain_residual_all_experts": dict(streams=0, experts=3, top=3, shared_ff=0, scaling=False, kv_heads=1, chunk=16),
     "block_longer_than_prompt": dict(chunk=500, n_layers=2, rot_dims=2),
     "no_positions_no_mask": dict(rot_dims=0, chunk=0, n_layers=2, streams=4),
-    # every matrix tile-aligned: with BF16 weights the projections and the shared expert run on the tensor cores
-    "tensor_core_tiles": dict(width=128, heads=2, kv_heads=2, dim=32, vdim=64, ff=64, shared_ff=128, n_layers=2, kv_from={1: 0}, chunk=24, rot_dims=16, streams=2),
+    # every matrix tile-aligned: with BF16 weights the projections, the routed experts and the shared expert run on the tensor cores
+    "tensor_core_tiles": dict(width=128, heads=2, kv_heads=2, dim=32, vdim=64, ff=128, shared_ff=128, n_layers=2, kv_from={1: 0}, chunk=24, rot_dims=16, streams=2),
+    # experts too narrow for a tile (gathered CUDA-core GEMMs) beside tile-aligned projections; an expert nobody chooses is likely with 9 of them
+    "mixed_tiles": dict(width=128, heads=2, kv_heads=1, dim=64, vdim=64, ff=40, shared_ff=128, experts=9, top=1, n_layers=2, chunk=33, rot_dims=64, streams=2),
 }
 
 

@@ -53,6 +53,25 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return v;
 }
 
+// element r of every stream of one token: X[t][r] <- sum_s M[s][t] X[s][r] + b[t] * v  (all t from the old values)
+__device__ __forceinline__ void streams_update(const StreamsIO& sio, int N, int r, float v) {
+    float xv[16], nv[16];
+#pragma unroll
+    for (int s = 0; s < 16; s++) xv[s] = s < sio.S ? sio.X_out[(size_t)s * N + r] : 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; t++) {
+        float acc = 0.f;
+        if (t < sio.S) {
+#pragma unroll
+            for (int s = 0; s < 16; s++) if (s < sio.S) acc = fmaf(sio.M[s * sio.S + t], xv[s], acc);
+            acc = fmaf(sio.b[t], v, acc);
+        }
+        nv[t] = acc;
+    }
+#pragma unroll
+    for (int t = 0; t < 16; t++) if (t < sio.S) sio.X_out[(size_t)t * N + r] = nv[t];
+}
+
 struct DenseMats {
     const unsigned char* W[3];
     float* y[3];
@@ -102,14 +121,21 @@ __device__ __forceinline__ float dense_row_dot(const unsigned char* row, const f
 template <typename T>
 __global__ void __launch_bounds__(DV_WARPS * 32) gemv_dense_kernel(DenseMats m, const float* __restrict__ x, int K, int ep,
                                                                    const float* __restrict__ row_scale, float alpha, int vec,
-                                                                   const float* __restrict__ norm_w, float eps) {
+                                                                   const float* __restrict__ norm_w, float eps, StreamsIO sio) {
     extern __shared__ __align__(16) float xs[];
     __shared__ float red[DV_WARPS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();
     float ss = 0.f;
-    for (int i = threadIdx.x; i < K; i += DV_WARPS * 32) { const float v = x[i]; xs[i] = v; ss = fmaf(v, v, ss); }
+    for (int i = threadIdx.x; i < K; i += DV_WARPS * 32) {
+        float v;
+        if (sio.X_in) {                   // the blend of the token's residual streams
+            v = 0.f;
+            for (int st = 0; st < sio.S; st++) { const float xv = sio.X_in[(size_t)st * K + i]; v = sio.a ? fmaf(sio.a[st], xv, v) : v + xv; }
+        } else v = x[i];
+        xs[i] = v; ss = fmaf(v, v, ss);
+    }
     if (norm_w) {
         // RMS norm of the staged vector: every CTA sums the squares in the same order, so all CTAs (and every launch that reads the
         // same x) derive the bit-identical normalised vector
@@ -136,7 +162,8 @@ __global__ void __launch_bounds__(DV_WARPS * 32) gemv_dense_kernel(DenseMats m, 
         int mi = 0, row = r;
         if (row >= m.out[0]) { row -= m.out[0]; mi = 1; if (row >= m.out[1]) { row -= m.out[1]; mi = 2; } }
         const float v = dense_row_dot<T>(m.W[mi] + (size_t)row * m.pitch[mi], xs, K, lane, vec);
-        if (lane == 0) {
+        if (lane == 0 && ep == DENSE_STREAMS) streams_update(sio, m.out[0], row, v);
+        else if (lane == 0) {
             float* y = m.y[mi] + row;
             if (ep == DENSE_ADD) *y += v;
             else if (ep == DENSE_SCALED_ADD) *y = fmaf(alpha * (row_scale ? row_scale[row] : 1.f), v, *y);
@@ -211,8 +238,11 @@ __global__ void to_f32_kernel(float* __restrict__ out, const T* __restrict__ in,
 bool dense_dtype(DType dt) { return dt == DType::F32 || dt == DType::F16 || dt == DType::BF16; }
 
 void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s,
-                const float* norm_w, float eps) {
+                const float* norm_w, float eps, const StreamsIO* sio_p) {
     NT_CHECK(n_mat >= 1 && n_mat <= 3, "gemv_dense: 1..3 matrices");
+    const StreamsIO sio = sio_p ? *sio_p : StreamsIO();
+    NT_CHECK(ep != DENSE_STREAMS || (n_mat == 1 && sio.X_out && sio.M && sio.b && sio.S >= 1 && sio.S <= 16), "gemv_dense: the streams epilogue takes one matrix and the stream tables");
+    NT_CHECK(!sio.X_in || (sio.S >= 1 && sio.S <= 16), "gemv_dense: 1..16 streams");
     const bool glu = ep == DENSE_SWIGLU || ep == DENSE_GEGLU;
     NT_CHECK(!glu || (n_mat == 2 && mats[0].out == mats[1].out), "gemv_dense: a gated epilogue takes two matrices of equal height");
     const DType dt = mats[0].dtype;
@@ -236,7 +266,7 @@ void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpil
     const int resident = (int)std::max<size_t>(1, std::min<size_t>(8, (size_t)(220 * 1024) / (smem + 1024))) * 148;
     grid = std::min(grid, resident);
 #define NT_DV(TY) { static unsigned long long done = 0; if (smem > 48 * 1024) opt_in_dynamic_smem(gemv_dense_kernel<TY>, 200 * 1024, done); \
-                    launch_k(gemv_dense_kernel<TY>, dim3(grid), dim3(DV_WARPS * 32), smem, s, m, x, K, (int)ep, row_scale, alpha, vec, norm_w, eps); }
+                    launch_k(gemv_dense_kernel<TY>, dim3(grid), dim3(DV_WARPS * 32), smem, s, m, x, K, (int)ep, row_scale, alpha, vec, norm_w, eps, sio); }
     if (dt == DType::F32) NT_DV(float) else if (dt == DType::F16) NT_DV(__half) else NT_DV(__nv_bfloat16)
 #undef NT_DV
     count_launch();

@@ -444,8 +444,9 @@ MoeWeights Model::moe_of(int i, bool with_shared) const {
     return w;
 }
 
-// One decoded token.  Launches: [read blend] [norm + q/k/v GEMV] [rotary + cache write] [attention, both maps] [differential combine]
-// [o GEMV] [stream write]   [read blend] [norm] [router] [experts up + relu^2] [experts down, weighted, + shared] [stream write]
+// One decoded token, 8 launches: [stream blend + norm + q/k/v GEMV] [rotary + cache write] [attention, both maps] [differential combine]
+// [o GEMV -> streams]   [stream blend + norm + router] [experts up + relu^2] [experts down, weighted, + shared -> streams]
+// The stream read lives in the prologue of the kernel that consumes it, the stream write in the epilogue of the one that produces y.
 void Model::layer_streams_token(int i, cudaStream_t s) {
     const LayerSpec& S = cfg_.layers[(size_t)i];
     const LayerWeights& L = layer_weights(i);
@@ -453,29 +454,28 @@ void Model::layer_streams_token(int i, cudaStream_t s) {
     const int* pos_dev = step_dev_ + 1;
     const bool one = cfg_.streams == 0;            // a single residual: identity tables
     const int qd = S.heads * S.maps * S.dim, kd = S.kv_heads * S.maps * S.dim, vd = S.kv_heads * S.vdim;
-    streams_read(xnorm_, streams_, one ? nullptr : L.hc_in[0], 1, NS, hidden, s);
+    StreamsIO rd; rd.X_in = streams_; rd.a = one ? nullptr : L.hc_in[0]; rd.S = NS;
     if (S.kv_from < 0) {
         GemvMat qkv[3] = {mat_of(L.wq, q_), mat_of(L.wk, k_), mat_of(L.wv, v_)};
-        gemv_dense(qkv, 3, hidden, xnorm_, DENSE_STORE, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps);
+        gemv_dense(qkv, 3, hidden, nullptr, DENSE_STORE, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps, &rd);
     } else {
         GemvMat q1 = mat_of(L.wq, q_);
-        gemv_dense(&q1, 1, hidden, xnorm_, DENSE_STORE, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps);
+        gemv_dense(&q1, 1, hidden, nullptr, DENSE_STORE, nullptr, 1.f, s, L.attn_norm, cfg_.norm_eps, &rd);
     }
     rope_partial_kv_write(q_, S.kv_from < 0 ? k_ : nullptr, v_, L.rot_freq, L.rot_mag, S.rot.dims, S.rot.interleaved, S.dim, kcs_[(size_t)i], vcs_[(size_t)i],
                           cache_dt_, 1, pos_dev, 0, qd, kd, vd, s);
     attention_window(S.maps > 1 ? maps_out_ : attn_, q_, kcs_[(size_t)i], vcs_[(size_t)i], cache_dt_, 1, pos_dev, 0, cfg_.max_seq_len, attn_of(S), s);
     if (S.maps > 1) diff_combine(attn_, maps_out_, L.lq1, L.lk1, L.lq2, L.lk2, S.dim, S.diff, cfg_.norm_eps, 1, S.heads, S.vdim, s);
-    GemvMat o = mat_of(L.wo, sub_y_);
-    gemv_dense(&o, 1, S.heads * S.vdim, attn_, DENSE_STORE, nullptr, 1.f, s);
-    streams_write(streams_, sub_y_, one ? ident_tab_ : L.hc_mix[0], one ? ident_tab_ : L.hc_out[0], 1, NS, hidden, s);
+    StreamsIO wr; wr.X_out = streams_; wr.M = one ? ident_tab_ : L.hc_mix[0]; wr.b = one ? ident_tab_ : L.hc_out[0]; wr.S = NS;
+    GemvMat o = mat_of(L.wo, nullptr);
+    gemv_dense(&o, 1, S.heads * S.vdim, attn_, DENSE_STREAMS, nullptr, 1.f, s, nullptr, 0.f, &wr);
     if (S.ff <= 0) return;
-    streams_read(xnorm_, streams_, one ? nullptr : L.hc_in[1], 1, NS, hidden, s);
-    rmsnorm(part_, xnorm_, L.ffn_norm, 1, hidden, cfg_.norm_eps, s);
+    rd.a = one ? nullptr : L.hc_in[1];
+    wr.M = one ? ident_tab_ : L.hc_mix[1]; wr.b = one ? ident_tab_ : L.hc_out[1];
     const MoeWeights w = moe_of(i, true);
-    moe_route(moe_sel_, moe_wt_, moe_sgate_, part_, w, 1, s);
+    moe_route(moe_sel_, moe_wt_, moe_sgate_, nullptr, w, 1, s, &rd, L.ffn_norm, cfg_.norm_eps, part_);
     moe_expert_up_token(moe_act_, part_, moe_sel_, w, s);
-    moe_expert_down_token(sub_y_, moe_act_, moe_sel_, moe_wt_, moe_sgate_, nullptr, w, s);
-    streams_write(streams_, sub_y_, one ? ident_tab_ : L.hc_mix[1], one ? ident_tab_ : L.hc_out[1], 1, NS, hidden, s);
+    moe_expert_down_token(nullptr, moe_act_, moe_sel_, moe_wt_, moe_sgate_, nullptr, w, s, &wr);
 }
 
 // T prompt rows at positions p0..: the same steps over rows; projections and the shared expert through spec_gemm (tensor cores

@@ -129,12 +129,21 @@ bool sample_topk(float* logits_dev, int n, float temperature, int top_k, float t
 
 // ---- dense.cu / attention_window.cu: kernels of the layer-spec model families (dense F32 / F16 / BF16 weights, F32 activations) ----
 enum DenseEpilogue { DENSE_STORE = 0, DENSE_ADD = 1, DENSE_SCALED_ADD = 2 /* y[r] += alpha * row_scale[r] * (W.x)[r]; row_scale may be null */,
-                     DENSE_SWIGLU = 3 /* y0 = silu(W0.x) * (W1.x) */, DENSE_GEGLU = 4 /* y0 = gelu_tanh(W0.x) * (W1.x) */ };
+                     DENSE_SWIGLU = 3 /* y0 = silu(W0.x) * (W1.x) */, DENSE_GEGLU = 4 /* y0 = gelu_tanh(W0.x) * (W1.x) */,
+                     DENSE_STREAMS = 5 /* one matrix; its output enters the residual streams: StreamsIO::X_out, y is not written */ };
+// Residual streams [S, n] of ONE token folded into a GEMV (decode).  Prologue (X_in given): the activation vector is
+// x[i] = sum_s a[s] * X_in[s * K + i] (a == null: the plain sum) instead of the x argument.  Epilogue DENSE_STREAMS: with v = (W.x)[r],
+// X_out[t * N + r] <- sum_s M[s * S + t] * X_out[s * N + r] + b[t] * v for every t (row r is owned by one warp, so the update is race-free).
+struct StreamsIO {
+    const float* X_in = nullptr; const float* a = nullptr;
+    float* X_out = nullptr; const float* M = nullptr; const float* b = nullptr;
+    int S = 0;
+};
 bool dense_dtype(DType dt);
 // Up to 3 matrices of one dense dtype sharing the activation vector x[K] (GemvMat::y: each matrix's output rows).
 // norm_w: the kernel's prologue first replaces x by x / sqrt(mean(x^2) + eps) * norm_w (the block's RMS norm, recomputed per CTA).
 void gemv_dense(const GemvMat* mats, int n_mat, int K, const float* x, DenseEpilogue ep, const float* row_scale, float alpha, cudaStream_t s,
-                const float* norm_w = nullptr, float eps = 0.f);
+                const float* norm_w = nullptr, float eps = 0.f, const StreamsIO* sio = nullptr);
 // C[T,N] (ep)= A[T,K] . W[N,K]^T in true FP32 on CUDA cores (store / add / scaled-add; row_scale indexes N).
 void gemm_dense(float* C, const float* A, const void* W, DType dt, size_t row_pitch, int T, int N, int K, DenseEpilogue ep,
                 const float* row_scale, float alpha, cudaStream_t s);
@@ -194,11 +203,15 @@ struct MoeWeights {
 };
 // Router: logits in F32, the `top` largest (lowest index on ties), softmax over the chosen -> sel [tokens, top], wt [tokens, top];
 // sgate [tokens] = sigmoid(<shared_gate, h>) when shared_gate is given.
-void moe_route(int* sel, float* wt, float* sgate, const float* h, const MoeWeights& w, int tokens, cudaStream_t s);
+// sio->X_in: the token's input is the blend of its residual streams ([tokens, S, width]) instead of h; norm_w: it is RMS-normalised
+// (times norm_w) first; h_out: the vector the router saw is written there for the expert kernels.
+void moe_route(int* sel, float* wt, float* sgate, const float* h, const MoeWeights& w, int tokens, cudaStream_t s,
+               const StreamsIO* sio = nullptr, const float* norm_w = nullptr, float eps = 0.f, float* h_out = nullptr);
 // One token (decode): act [top * ff + shared_ff] = relu(W_up[sel] h)^2 ; y [width] = sum_k wt[k] * W_down[sel[k]] act[k] + sgate * shared part.
 void moe_expert_up_token(float* act, const float* h, const int* sel, const MoeWeights& w, cudaStream_t s);
+// sio->X_out: the result enters the residual streams (StreamsIO) instead of y.
 void moe_expert_down_token(float* y, const float* act, const int* sel, const float* wt, const float* sgate, const float* shared_y,
-                           const MoeWeights& w, cudaStream_t s);
+                           const MoeWeights& w, cudaStream_t s, const StreamsIO* sio = nullptr);
 // Prompt rows: assignments grouped per expert (order inside an expert = token order), gathered GEMMs on CUDA cores in F32.
 //   work: ints [experts + 1 (offsets) + tokens*top (row -> token) + tokens*top (assignment -> row)]
 size_t moe_work_ints(int tokens, int experts, int top);

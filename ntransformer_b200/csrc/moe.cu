@@ -91,15 +91,36 @@ constexpr int MAX_EXPERTS = 256;
 
 __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(int* __restrict__ sel, float* __restrict__ wt, float* __restrict__ sgate,
                                                                   const float* __restrict__ h, const float* __restrict__ router,
-                                                                  const float* __restrict__ shared_gate, int experts, int top, int width) {
+                                                                  const float* __restrict__ shared_gate, int experts, int top, int width,
+                                                                  StreamsIO sio, const float* __restrict__ norm_w, float eps, float* __restrict__ h_out) {
     extern __shared__ __align__(16) float hs[];
     __shared__ float z[MAX_EXPERTS + 1];
+    __shared__ float red[RT_WARPS];
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     pdl_wait();
-    const float* x = h + (size_t)t * width;
-    for (int i = threadIdx.x; i < width; i += RT_WARPS * 32) hs[i] = x[i];
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += RT_WARPS * 32) {
+        float v;
+        if (sio.X_in) {                   // the blend of the token's residual streams
+            v = 0.f;
+            for (int st = 0; st < sio.S; st++) { const float xv = sio.X_in[((size_t)t * sio.S + st) * width + i]; v = sio.a ? fmaf(sio.a[st], xv, v) : v + xv; }
+        } else v = h[(size_t)t * width + i];
+        hs[i] = v; ss = fmaf(v, v, ss);
+    }
+    if (norm_w) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < RT_WARPS; w++) tot += red[w];
+        const float inv = 1.0f / sqrtf(tot / (float)width + eps);
+        for (int i = threadIdx.x; i < width; i += RT_WARPS * 32) hs[i] = hs[i] * inv * norm_w[i];
+    }
     __syncthreads();
+    if (h_out) for (int i = threadIdx.x; i < width; i += RT_WARPS * 32) h_out[(size_t)t * width + i] = hs[i];
     const bool vec = width % 4 == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0;
     const int rows = experts + (shared_gate ? 1 : 0);
     for (int e = warp; e < rows; e += RT_WARPS) {
@@ -158,7 +179,7 @@ __global__ void __launch_bounds__(TK_WARPS * 32) moe_up_token_kernel(float* __re
 }
 template <typename T>
 __global__ void __launch_bounds__(TK_WARPS * 32) moe_down_token_kernel(float* __restrict__ y, const float* __restrict__ act, const int* __restrict__ sel,
-                                                                       const float* __restrict__ wt, const float* __restrict__ sgate, MoeDev m) {
+                                                                       const float* __restrict__ wt, const float* __restrict__ sgate, MoeDev m, StreamsIO sio) {
     extern __shared__ __align__(16) float as[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
@@ -177,7 +198,26 @@ __global__ void __launch_bounds__(TK_WARPS * 32) moe_down_token_kernel(float* __
             const unsigned char* wr = static_cast<const unsigned char*>(m.shared_down) + (size_t)r * m.shared_ff * sizeof(T);
             acc = fmaf(sgate[0], warp_dot<T>(wr, as + (size_t)m.top * m.ff, m.shared_ff, lane, svec && (reinterpret_cast<uintptr_t>(wr) & 15) == 0 && (((size_t)m.top * m.ff) & 3) == 0), acc);
         }
-        if (lane == 0) y[r] = acc;
+        if (lane == 0) {
+            if (!sio.X_out) y[r] = acc;
+            else {                        // X[t][r] <- sum_s M[s][t] X[s][r] + b[t] * acc, all t from the old values
+                float xv[16], nv[16];
+#pragma unroll
+                for (int s = 0; s < 16; s++) xv[s] = s < sio.S ? sio.X_out[(size_t)s * m.width + r] : 0.f;
+#pragma unroll
+                for (int t = 0; t < 16; t++) {
+                    float a2 = 0.f;
+                    if (t < sio.S) {
+#pragma unroll
+                        for (int s = 0; s < 16; s++) if (s < sio.S) a2 = fmaf(sio.M[s * sio.S + t], xv[s], a2);
+                        a2 = fmaf(sio.b[t], acc, a2);
+                    }
+                    nv[t] = a2;
+                }
+#pragma unroll
+                for (int t = 0; t < 16; t++) if (t < sio.S) sio.X_out[(size_t)t * m.width + r] = nv[t];
+            }
+        }
     }
 }
 
@@ -304,14 +344,16 @@ MoeDev dev_of(const MoeWeights& w) { return MoeDev{w.up, w.down, w.shared_up, w.
 
 }  // namespace
 
-void moe_route(int* sel, float* wt, float* sgate, const float* h, const MoeWeights& w, int tokens, cudaStream_t s) {
+void moe_route(int* sel, float* wt, float* sgate, const float* h, const MoeWeights& w, int tokens, cudaStream_t s, const StreamsIO* sio_p,
+               const float* norm_w, float eps, float* h_out) {
+    const StreamsIO sio = sio_p ? *sio_p : StreamsIO();
     NT_CHECK(w.experts >= 1 && w.experts <= MAX_EXPERTS && w.top >= 1 && w.top <= w.experts, "moe_route: 1 <= top <= experts <= 256");
     if (tokens <= 0) return;
     const size_t smem = (size_t)w.width * sizeof(float);
     NT_CHECK(smem <= 160 * 1024, "moe_route: the activation row does not fit in shared memory");
     static unsigned long long done = 0;
     if (smem > 40 * 1024) opt_in_dynamic_smem(moe_route_kernel, 160 * 1024, done);
-    launch_k(moe_route_kernel, dim3(tokens), dim3(RT_WARPS * 32), smem, s, sel, wt, sgate, h, w.router, w.shared_gate, w.experts, w.top, w.width);
+    launch_k(moe_route_kernel, dim3(tokens), dim3(RT_WARPS * 32), smem, s, sel, wt, sgate, h, w.router, w.shared_gate, w.experts, w.top, w.width, sio, norm_w, eps, h_out);
     count_launch();
 }
 
@@ -333,13 +375,14 @@ void moe_expert_up_token(float* act, const float* h, const int* sel, const MoeWe
 }
 
 void moe_expert_down_token(float* y, const float* act, const int* sel, const float* wt, const float* sgate, const float* /*shared_y*/,
-                           const MoeWeights& w, cudaStream_t s) {
+                           const MoeWeights& w, cudaStream_t s, const StreamsIO* sio_p) {
     const MoeDev m = dev_of(w);
+    const StreamsIO sio = sio_p ? *sio_p : StreamsIO();
     const size_t smem = (size_t)(m.top * m.ff + m.shared_ff) * sizeof(float);
     NT_CHECK(smem <= 200 * 1024, "moe: the chosen experts' activations do not fit in shared memory");
     const int grid = std::min((w.width + TK_WARPS - 1) / TK_WARPS, 148 * 8);
 #define NT_CALL(TY) { static unsigned long long done = 0; if (smem > 48 * 1024) opt_in_dynamic_smem(moe_down_token_kernel<TY>, 200 * 1024, done); \
-                      launch_k(moe_down_token_kernel<TY>, dim3(grid), dim3(TK_WARPS * 32), smem, s, y, act, sel, wt, sgate, m); }
+                      launch_k(moe_down_token_kernel<TY>, dim3(grid), dim3(TK_WARPS * 32), smem, s, y, act, sel, wt, sgate, m, sio); }
     NT_MOE_DT(NT_CALL)
 #undef NT_CALL
     count_launch();

@@ -233,23 +233,36 @@ __global__ void moe_count_kernel(int* __restrict__ work, const int* __restrict__
     for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
     if (lane == 0) work[experts + 1 + 2 * (size_t)n + e] = c;      // counts live behind the two tables
 }
-__global__ void moe_place_kernel(int* __restrict__ work, const int* __restrict__ sel, int n, int experts, int top) {
+constexpr int PL_WARPS = 8;
+// One CTA per expert; its warps take consecutive slices of the assignments: count per slice, prefix over the slices, then an
+// ordered placement inside each slice (ballot + popc), so rows of an expert stay in assignment (= token) order.
+__global__ void __launch_bounds__(PL_WARPS * 32) moe_place_kernel(int* __restrict__ work, const int* __restrict__ sel, int n, int experts, int top) {
+    __shared__ int slice_count[PL_WARPS];
     pdl_launch_dependents();
     pdl_wait();
-    const int e = blockIdx.x, lane = threadIdx.x;
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* counts = work + experts + 1 + 2 * (size_t)n;
     int off = 0;
     for (int x = 0; x < e; x++) off += counts[x];
     int* row_token = work + experts + 1;
     int* assign_row = row_token + n;
-    if (lane == 0) { work[e] = off; if (e == experts - 1) work[experts] = off + counts[e]; }
-    int placed = 0;
-    for (int a0 = 0; a0 < n; a0 += 32) {
+    if (threadIdx.x == 0) { work[e] = off; if (e == experts - 1) work[experts] = off + counts[e]; }
+    const int per = ((n + PL_WARPS - 1) / PL_WARPS + 31) / 32 * 32;
+    const int a_begin = min(n, warp * per), a_end = min(n, a_begin + per);
+    int c = 0;
+    for (int a = a_begin + lane; a < a_end; a += 32) c += sel[a] == e ? 1 : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+    if (lane == 0) slice_count[warp] = c;
+    __syncthreads();
+    int placed = off;
+    for (int w = 0; w < warp; w++) placed += slice_count[w];
+    for (int a0 = a_begin; a0 < a_end; a0 += 32) {
         const int a = a0 + lane;
-        const bool mine = a < n && sel[a] == e;
+        const bool mine = a < a_end && sel[a] == e;
         const unsigned m = __ballot_sync(0xFFFFFFFFu, mine);
         if (mine) {
-            const int row = off + placed + __popc(m & ((1u << lane) - 1u));
+            const int row = placed + __popc(m & ((1u << lane) - 1u));
             row_token[row] = a / top;
             assign_row[a] = row;
         }
@@ -393,7 +406,7 @@ size_t moe_work_ints(int tokens, int experts, int top) { return (size_t)experts 
 void moe_group(int* work, const int* sel, int tokens, int experts, int top, cudaStream_t s) {
     if (tokens <= 0) return;
     launch_k(moe_count_kernel, dim3(experts), dim3(32), 0, s, work, sel, tokens * top, experts);
-    launch_k(moe_place_kernel, dim3(experts), dim3(32), 0, s, work, sel, tokens * top, experts, top);
+    launch_k(moe_place_kernel, dim3(experts), dim3(PL_WARPS * 32), 0, s, work, sel, tokens * top, experts, top);
     count_launch(2);
 }
 

@@ -110,6 +110,22 @@ def test_attention_maps_tiled_form(H, G, maps, dim, vdim, chunk):
         np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("cache", [DType.F32, DType.BF16])
+def test_decoded_token_over_long_blocks(cache):
+    """A single decoded token in a block of hundreds of positions: its keys are split over a cluster of CTAs and merged."""
+    rng = np.random.default_rng(17)
+    H, G, maps, dim, vdim, chunk, n = 2, 1, 2, 16, 24, 600, 1000
+    tdt = torch.float32 if cache == DType.F32 else torch.bfloat16
+    kc = dev(rng.standard_normal((n, G * maps * dim)), tdt); vc = dev(rng.standard_normal((n, G * vdim)), tdt)
+    k = kc.double().cpu().numpy(); v = vc.double().cpu().numpy()
+    for pos in (599, 600, 601, 999, 350):
+        q = rng.standard_normal(H * maps * dim)
+        Q = dev(q[None]); out = torch.zeros(1, H * maps * vdim, device="cuda")
+        lib().nt_b200_attention_maps(out.data_ptr(), Q.data_ptr(), kc.data_ptr(), vc.data_ptr(), int(cache), 1, pos, H, G, dim, vdim, chunk, maps, 0.3, n, stream())
+        ref = maps_reference(q, k, v, pos, H, G, maps, dim, vdim, chunk, 0.3).reshape(-1)
+        np.testing.assert_allclose(out[0].cpu().numpy(), ref, rtol=3e-5, atol=3e-5)
+
+
 @pytest.mark.parametrize("tokens_at_once", [True, False])
 def test_block_edges_with_one_loud_key(tokens_at_once):
     """Among hundreds of quiet keys, a key aligned with the query wins the softmax when it sits on the first row of the query's block,
